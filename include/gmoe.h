@@ -1,0 +1,90 @@
+/* gmoe.h -- entry points this library ADDS next to the reference's plug-in ABI (gpre.h).
+ *
+ * The reference keeps softmax/top-8 and the grouping of pairs on the host between two GPU calls
+ * (maple.c:1015-1021).  Here the whole mixture-of-experts half of a layer runs on the device:
+ *   RMSNorm (maple.c:398-402) -> per-token absmax int8 (184-194) -> router logits (870-889) -> softmax + top-8
+ *   (910-923) -> grouping by expert (924-938, 1018-1019) -> gate+up (471-479, 425-458) -> SiLU*up + per-pair int8
+ *   (825-832) -> down (498-505) -> weighted combine into the hidden state (834).
+ * Plain C ABI: pointers and sizes only.  Host pointers unless a name says _dev.
+ * Every int-returning function returns 0 on success and -1 after a "gmoe: ..." line on stderr;
+ * gmoe_last_error() returns that line.
+ */
+#ifndef GMOE_H
+#define GMOE_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GMOE_LAYERS 24
+#define GMOE_MAXTOK_LIMIT 16384
+
+/* ---- set-up ------------------------------------------------------------------------------------------------ */
+/* Same as gpre_init(maxtok, 8) (maple.c:1105) plus the routing workspace; maxtok <= GMOE_MAXTOK_LIMIT. */
+int gmoe_init(int maxtok);
+/* Selects the CUDA device of this process (call before gmoe_init / gpre_init; one process per GPU). */
+int gmoe_set_device(int dev);
+/* Layer L's tables in the reference's own form: router bf16 [256][2048] (Layer.router, maple.c:39), post-attention
+ * RMSNorm weight bf16 [2048] (Layer.post_ln), gloc = GLOC[L] [256][12] and regs = GREG[L] [4] as maple.c:1106-1131
+ * builds them for regions registered with gpre_region.  post_ln may be NULL when only normalised input is used. */
+int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const uint32_t *gloc, const int *regs);
+/* Synthetic layer L generated in HBM by the device generator (synth.h), registered like gmoe_set_layer.
+ * e0/ne: only experts e0..e0+ne-1 are materialised (expert-parallel shards); e0 = 0, ne = 256 for all. */
+int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne);
+
+/* ---- one layer, host buffers (the drop-in shape of gpre_moe with routing on the device) ---------------------- */
+/* x [nb][2048] normalised hidden state; y [nb][2048] = sum_k w_k expert_k(x), no residual; bias [256] added to
+ * the router logits before the softmax (NULL = none; the reference has no bias, benchmarks use it for skew).
+ * Synchronous; returns GPU seconds or a negative value. */
+double gmoe_moe(int L, const float *x, int nb, float *y, const float *bias);
+
+/* ---- the residual stream through nl layers starting at l0 ----------------------------------------------------- */
+/* Host in/out: per layer hn = rmsnorm(x, post_ln), x += moe(hn) (maple.c:733-834).  Returns GPU seconds. */
+double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias);
+/* Device-resident form: upload once, run (asynchronous, on the library's stream), download. */
+int gmoe_x_upload(const float *x, int nb);
+int gmoe_x_download(float *x, int nb);
+int gmoe_forward_dev(int nb, int l0, int nl, const float *bias);
+/* Waits for the stream; returns the GPU seconds between the last gmoe_forward_dev's first and last kernel. */
+double gmoe_sync(void);
+/* rmsnorm(post_ln[L]) of the device-resident hidden state + int8 + router logits: the part of gfull_attn
+ * (gpu_pre.m:486-501) that feeds the experts.  logits [nb][256] may be NULL. Synchronous. */
+int gmoe_post_norm(int L, int nb, float *logits);
+
+/* ---- parity hooks: named device buffers of the last call, and single stages ---------------------------------- */
+/* Names: x hn y hq hqs hqsum logits top topw nu ue ustart utok uw tp gate up act aq aqs aqsum down gu_dots dn_dots */
+int gmoe_peek(const char *name, void *dst, size_t bytes);
+int gmoe_poke(const char *name, const void *src, size_t bytes);
+/* keep = 1: the expert kernels also store gate, up and the int32 dot products (tot - qsum). */
+int gmoe_keep_stages(int keep);
+/* Runs one stage on the device buffers for nb tokens of layer L: "norm" (x->hn,hq..), "prep" (hn->hq..),
+ * "router", "topk", "group", "gateup", "actq", "down", "combine_y" (y = sum), "combine_x" (x += sum). */
+int gmoe_stage(const char *name, int L, int nb);
+/* 0 = grouped kernels chosen by size (default), 1 = force the mma.sync register-decode kernels,
+ * 2 = force the tcgen05 kernels. */
+int gmoe_set_path(int path);
+/* Copies bytes [off, off+bytes) of a registered region (gpre_region id, or the id a synthetic layer got: regions are
+ * numbered in registration order) back to the host, to check what lives in HBM. */
+int gmoe_region_read(int region, size_t off, void *dst, size_t bytes);
+int gmoe_region_count(void);
+
+/* ---- utilities -------------------------------------------------------------------------------------------------- */
+const char *gmoe_last_error(void);
+long gmoe_launch_count(void);             /* kernels launched by this library since load */
+void *gmoe_pinned_alloc(size_t bytes);    /* page-locked host memory for x/y so copies overlap */
+void gmoe_pinned_free(void *p);
+int gmoe_device_info(char *name, int namelen, int *sms, size_t *hbm_bytes);
+
+/* ---- synthetic workload (host side; synth.h gives the generator) ------------------------------------------------ */
+void msynth_expert(uint64_t seed, int L, int e, uint8_t *dst);                 /* 798,720 bytes */
+void msynth_experts(uint64_t seed, int L, int e0, int ne, uint8_t *dst);
+void msynth_router(uint64_t seed, int L, uint16_t *dst);                       /* bf16 [256][2048] */
+void msynth_norm(uint64_t seed, int L, uint16_t *dst);                         /* bf16 [2048] */
+void msynth_hidden(uint64_t seed, uint64_t stream, int nb, float *dst);        /* fp32 [nb][2048] ~ N(0,1) */
+void msynth_zipf_bias(uint64_t seed, double s, float *bias);                   /* fp32 [256] */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

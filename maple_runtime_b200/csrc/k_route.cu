@@ -1,0 +1,382 @@
+// k_route.cu -- everything of the MoE half that is not a grouped GEMM: RMSNorm + per-token int8, router logits,
+// softmax + top-8, grouping of pairs by expert, SiLU-output int8, weighted combine.  sm_100a.
+//
+// Every kernel reproduces the reference's arithmetic operation by operation (order of additions, fused
+// multiply-adds where the reference fuses, IEEE division and round-half-even), so its integer outputs are equal
+// and its fp32 outputs are the same bits as maple.c's CPU path.  File:line citations are into maple.c.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "kernels.h"
+#include "dev_math.cuh"
+
+static long g_launches = 0;
+extern "C" void k_count_reset(void) { g_launches = 0; }
+extern "C" long k_count(void) { return g_launches; }
+extern "C" void k_count_add(long n) { g_launches += n; }
+
+#define HID 2048
+#define NEXP 256
+#define TOPK 8
+#define FFN 512
+
+// ------------------------------------------------------------------------------------------------------------
+// RMSNorm (maple.c:398-402) + prep (maple.c:184-194), one CTA of 256 threads per token, 8 columns per thread.
+// w == NULL: x is already normalised (hn = x, not rewritten when hn == x).
+// The sum of squares is accumulated in double like the reference; the tree order differs from its left-to-right
+// order only below double precision, which the conversion to float absorbs.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w,
+                                                        float *__restrict__ hn, int8_t *__restrict__ q,
+                                                        float *__restrict__ qs, int *__restrict__ qsum) {
+    __shared__ double sd[8];
+    __shared__ float sf[8];
+    __shared__ int si[8];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)b * HID) + tid * 2;
+    float4 v0 = xr[0], v1 = xr[1];
+    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (w) {
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss += (double)v[i] * (double)v[i];
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sd[wid] = ss;
+        __syncthreads();
+        double tot = ((sd[0] + sd[1]) + (sd[2] + sd[3])) + ((sd[4] + sd[5]) + (sd[6] + sd[7]));
+        float k = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)HID), 1e-6f)));
+        const uint4 wr = reinterpret_cast<const uint4 *>(w)[tid];   // 8 bf16
+        const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float wf = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xFFFF0000u) : (ww[i >> 1] << 16));
+            v[i] = __fmul_rn(__fmul_rn(v[i], k), wf);
+        }
+        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + tid * 2;
+        hr[0] = make_float4(v[0], v[1], v[2], v[3]); hr[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else if (hn != x) {
+        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + tid * 2;
+        hr[0] = v0; hr[1] = v1;
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) sf[wid] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3])), fmaxf(fmaxf(sf[4], sf[5]), fmaxf(sf[6], sf[7])));
+    const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
+    int tot = 0; uint32_t pk[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int qi = __float2int_rn(__fmul_rn(v[i], inv));
+        tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3));
+    }
+    reinterpret_cast<uint2 *>(q + (size_t)b * HID)[tid] = make_uint2(pk[0], pk[1]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (lane == 0) si[wid] = tot;
+    __syncthreads();
+    if (tid == 0) { qs[b] = s; qsum[b] = si[0] + si[1] + si[2] + si[3] + si[4] + si[5] + si[6] + si[7]; }
+}
+extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb) {
+    if (nb <= 0) return;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum); g_launches++;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Router logits (maple.c:870-889 job_route_multi, 853-869 job_route_small): logit[b][e] = sum_c W[e][c]*hn[b][c]
+// in the reference's order: lane j of eight accumulates columns j, j+8, ... with one FMA each, and the eight
+// partial sums are added as ((l0+l4)+(l1+l5))+((l2+l6)+(l3+l7)) (hsum, maple.c:117-121).
+// 256 threads = 8 lanes x 32 tile positions; each thread owns a TT x TE register tile for its lane.
+// Shared-memory rows hold 128 columns re-ordered as [lane j][16 steps], lanes 20 floats apart so that the eight
+// lanes of one position read 128 distinct bytes per 16-byte access.
+// ------------------------------------------------------------------------------------------------------------
+#define RT_KC 128
+#define RT_LS 20
+#define RT_ROW (8 * RT_LS + 4)
+template <int TT, int TE, int PT, int PE>
+__global__ void __launch_bounds__(256) router_logits_kernel(const uint16_t *__restrict__ W, const float *__restrict__ hn,
+                                                            const float *__restrict__ bias, float *__restrict__ logits, int nb) {
+    constexpr int BT = TT * PT, BE = TE * PE;
+    static_assert(PT * PE == 32, "32 tile positions");
+    __shared__ __align__(16) float hs[BT * RT_ROW];
+    __shared__ __align__(16) float ws[BE * RT_ROW];
+    const int tid = threadIdx.x, j = tid & 7, pos = tid >> 3, pt = pos % PT, pe = pos / PT;
+    const int b0 = blockIdx.y * BT, e0 = blockIdx.x * BE;
+    float acc[TT][TE];
+#pragma unroll
+    for (int a = 0; a < TT; a++)
+#pragma unroll
+        for (int c = 0; c < TE; c++) acc[a][c] = 0.0f;
+
+    for (int c0 = 0; c0 < HID; c0 += RT_KC) {
+        __syncthreads();
+        // hidden tile: BT rows x 128 fp32, float4 per access
+        for (int i = tid; i < BT * (RT_KC / 4); i += 256) {
+            int r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b0 + r < nb) v = *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c);
+            float *d = hs + r * RT_ROW + (c >> 3);
+            int jj = c & 7;
+            d[(jj + 0) * RT_LS] = v.x; d[(jj + 1) * RT_LS] = v.y; d[(jj + 2) * RT_LS] = v.z; d[(jj + 3) * RT_LS] = v.w;
+        }
+        // router tile: BE rows x 128 bf16, eight per access
+        for (int i = tid; i < BE * (RT_KC / 8); i += 256) {
+            int r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
+            uint4 v = *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c);
+            float *d = ws + r * RT_ROW + (c >> 3);
+            d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
+            d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
+            d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
+            d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i4 = 0; i4 < RT_KC / 8 / 4; i4++) {
+            float4 hv[TT], wv[TE];
+#pragma unroll
+            for (int a = 0; a < TT; a++) hv[a] = *reinterpret_cast<const float4 *>(hs + (pt * TT + a) * RT_ROW + j * RT_LS + i4 * 4);
+#pragma unroll
+            for (int c = 0; c < TE; c++) wv[c] = *reinterpret_cast<const float4 *>(ws + (pe * TE + c) * RT_ROW + j * RT_LS + i4 * 4);
+#pragma unroll
+            for (int a = 0; a < TT; a++)
+#pragma unroll
+                for (int c = 0; c < TE; c++) {
+                    acc[a][c] = __fmaf_rn(wv[c].x, hv[a].x, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].y, hv[a].y, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].z, hv[a].z, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].w, hv[a].w, acc[a][c]);
+                }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < TT; a++)
+#pragma unroll
+        for (int c = 0; c < TE; c++) {
+            float l = acc[a][c];
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 4));   // l_j + l_{j^4}
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 1));   // (l0+l4)+(l1+l5) | (l2+l6)+(l3+l7)
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 2));
+            int b = b0 + pt * TT + a, e = e0 + pe * TE + c;
+            if (j == 0 && b < nb) logits[(size_t)b * NEXP + e] = bias ? __fadd_rn(l, bias[e]) : l;
+        }
+}
+extern "C" void k_router_logits(cudaStream_t st, const uint16_t *router, const float *hn, const float *bias, float *logits, int nb) {
+    if (nb <= 0) return;
+    if (nb <= 256) {   // few tokens: small tiles so that the grid still covers the SMs
+        dim3 grid(NEXP / 8, (nb + 7) / 8);
+        router_logits_kernel<1, 2, 8, 4><<<grid, 256, 0, st>>>(router, hn, bias, logits, nb);
+    } else {
+        dim3 grid(NEXP / 32, (nb + 31) / 32);
+        router_logits_kernel<4, 8, 8, 4><<<grid, 256, 0, st>>>(router, hn, bias, logits, nb);
+    }
+    g_launches++;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Softmax + top-8 (maple.c:910-923): one warp per token, lane l holds experts 8l..8l+7.
+// p = expf(l - max); the sum runs over experts in index order (a chain through the lanes); p /= sum; eight rounds
+// of "first strict maximum" (lowest index wins a tie); weights divided by (their sum in selection order + 1e-20f).
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ logits, int *__restrict__ top, float *__restrict__ topw, int nb) {
+    const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (b >= nb) return;
+    const float4 *lr = reinterpret_cast<const float4 *>(logits + (size_t)b * NEXP + lane * 8);
+    float4 v0 = lr[0], v1 = lr[1];
+    float p[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float mx = -1e30f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx = p[i] > mx ? p[i] : mx;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, mx, o); mx = t > mx ? t : mx; }
+#pragma unroll
+    for (int i = 0; i < 8; i++) p[i] = dev_expf(__fsub_rn(p[i], mx));
+    float run = 0.0f;
+    for (int l = 0; l < 32; l++) {
+        if (lane == l) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) run = __fadd_rn(run, p[i]);
+        }
+        run = __shfl_sync(0xffffffffu, run, l);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) p[i] = __fdiv_rn(p[i], run);
+    float tsum = 0.0f, wsel = 0.0f; int isel = 0;
+    for (int k = 0; k < TOPK; k++) {
+        float bv = p[0]; int bi = 0;
+#pragma unroll
+        for (int i = 1; i < 8; i++) if (p[i] > bv) { bv = p[i]; bi = i; }
+        int be = lane * 8 + bi;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if ((be >> 3) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) if (i == (be & 7)) p[i] = -1.0f;
+        }
+        tsum = __fadd_rn(tsum, bv);
+        if (lane == k) { wsel = bv; isel = be; }
+    }
+    if (lane < TOPK) {
+        top[b * TOPK + lane] = isel;
+        topw[b * TOPK + lane] = __fdiv_rn(wsel, __fadd_rn(tsum, 1e-20f));
+    }
+}
+extern "C" void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb) {
+    if (nb <= 0) return;
+    topk_kernel<<<(nb + 7) / 8, 256, 0, st>>>(logits, top, topw, nb); g_launches++;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Grouping (maple.c:924-938) and tp (maple.c:1018-1019), deterministic without ordered atomics:
+//   1. mark:  bit b of mask[e] is set when token b chose expert e (atomicOr: the result does not depend on order)
+//   2. scan:  one CTA, thread e counts its bits; used experts are numbered in ascending order (NU, UE, USTART)
+//             and the tile lists for the grouped GEMMs are written
+//   3. fill:  one warp per expert walks its bits in token order: pair slot = USTART[u] + rank; UTOK, UW, and the
+//             slot of every (token, choice)
+//   4. tp:    per token the eight slots sorted ascending (pair index order = expert order)
+// ------------------------------------------------------------------------------------------------------------
+__global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restrict__ mask, int mask_words, int np) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= np) return;
+    int b = i >> 3, e = top[i];
+    atomicOr(&mask[(size_t)e * mask_words + (b >> 5)], 1u << (b & 31));
+}
+__global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__restrict__ mask, int mask_words, int *__restrict__ nu_out,
+                                                          int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart,
+                                                          MoeTile *__restrict__ ta, int *__restrict__ nta, int tna,
+                                                          MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb) {
+    __shared__ int s_cnt[NEXP], s_used[NEXP], s_ta[NEXP], s_tb[NEXP];
+    __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
+    const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
+    int cnt = 0;
+    for (int w = 0; w < mask_words; w++) cnt += __popc(mask[(size_t)e * mask_words + w]);
+    int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
+    // inclusive warp scans of the four quantities
+    int c = cnt, u = used, a = na, b = nb_;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int tc = __shfl_up_sync(0xffffffffu, c, o), tu = __shfl_up_sync(0xffffffffu, u, o);
+        int t1 = __shfl_up_sync(0xffffffffu, a, o), t2 = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) { c += tc; u += tu; a += t1; b += t2; }
+    }
+    if (lane == 31) { w_cnt[wid] = c; w_used[wid] = u; w_ta[wid] = a; w_tb[wid] = b; }
+    __syncthreads();
+    int oc = 0, ou = 0, oa = 0, ob = 0;
+    for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
+    s_cnt[e] = oc + c - cnt; s_used[e] = ou + u - used; s_ta[e] = oa + a - na; s_tb[e] = ob + b - nb_;   // exclusive
+    const int start = s_cnt[e], uidx = s_used[e];
+    estart[e] = used ? start : -1;
+    if (used) {
+        ue[uidx] = e; ustart[uidx] = start;
+        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * tna, min(tna, cnt - t * tna), 0}; ta[s_ta[e] + t] = m; }
+        for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * tnb, min(tnb, cnt - t * tnb), 0}; tb[s_tb[e] + t] = m; }
+    }
+    if (e == NEXP - 1) {
+        int nu = uidx + used;
+        *nu_out = nu; ustart[nu] = start + cnt; *nta = s_ta[e] + na; *ntb = s_tb[e] + nb_;
+    }
+}
+__global__ void __launch_bounds__(256) group_fill_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ estart,
+                                                         const int *__restrict__ top, const float *__restrict__ topw,
+                                                         int *__restrict__ utok, float *__restrict__ uw, int *__restrict__ slot) {
+    const int lane = threadIdx.x & 31, e = blockIdx.x * 8 + (threadIdx.x >> 5);
+    int base = estart[e];
+    if (base < 0) return;
+    for (int w0 = 0; w0 < mask_words; w0 += 32) {
+        unsigned m = (w0 + lane < mask_words) ? mask[(size_t)e * mask_words + w0 + lane] : 0u;
+        int c = __popc(m), incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+        int r = base + incl - c;
+        while (m) {
+            int bit = __ffs(m) - 1; m &= m - 1;
+            int b = (w0 + lane) * 32 + bit, s = 0;
+#pragma unroll
+            for (int k = 0; k < TOPK; k++) if (top[b * TOPK + k] == e) s = k;
+            utok[r] = b; uw[r] = topw[b * TOPK + s]; slot[b * TOPK + s] = r; r++;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+__global__ void group_tp_kernel(const int *__restrict__ slot, int *__restrict__ tp, int nb) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nb) return;
+    int s[TOPK];
+#pragma unroll
+    for (int k = 0; k < TOPK; k++) s[k] = slot[b * TOPK + k];
+#pragma unroll
+    for (int i = 1; i < TOPK; i++)
+#pragma unroll
+        for (int k = TOPK - 1; k >= 1; k--) if (k >= i && s[k] < s[k - 1]) { int t = s[k]; s[k] = s[k - 1]; s[k - 1] = t; }
+#pragma unroll
+    for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = s[k];
+}
+extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
+    if (g->nb <= 0) return;
+    const int np = g->nb * TOPK;
+    cudaMemsetAsync(g->mask, 0, (size_t)NEXP * g->mask_words * sizeof(unsigned), st);
+    group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
+    group_scan_kernel<<<1, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart,
+                                          g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b);
+    group_fill_kernel<<<NEXP / 8, 256, 0, st>>>(g->mask, g->mask_words, g->estart, g->top, g->topw, g->utok, g->uw, g->slot);
+    group_tp_kernel<<<(g->nb + 127) / 128, 128, 0, st>>>(g->slot, g->tp, g->nb);
+    g_launches += 4;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// SiLU-output int8 (the prep call of maple.c:831 on 512 values): one warp per pair, 16 values per lane.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) actq_kernel(const float *__restrict__ act, int8_t *__restrict__ aq, float *__restrict__ aqs,
+                                                   int *__restrict__ aqsum, int np) {
+    const int lane = threadIdx.x & 31, a = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (a >= np) return;
+    const float4 *r = reinterpret_cast<const float4 *>(act + (size_t)a * FFN) + lane * 4;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { float4 t = r[i]; v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w; }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
+    int tot = 0; uint32_t pk[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; i++) { int qi = __float2int_rn(__fmul_rn(v[i], inv)); tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3)); }
+    reinterpret_cast<uint4 *>(aq + (size_t)a * FFN)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (lane == 0) { aqs[a] = s; aqsum[a] = tot; }
+}
+extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max) {
+    (void)np_dev;
+    if (np_max <= 0) return;
+    actq_kernel<<<(np_max + 7) / 8, 256, 0, st>>>(act, aq, aqs, aqsum, np_max); g_launches++;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Combine (maple.c:834): out[b] = init[b] (or 0) then, for the token's pairs in ascending pair order,
+// out = fma(w, down, out) -- the order and the fused rounding of the reference's compiled loop.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ down, const float *__restrict__ uw, const int *__restrict__ tp,
+                                                      const float *__restrict__ init, float *__restrict__ out, int nb) {
+    const int i = blockIdx.x * 256 + threadIdx.x, b = i >> 9, c = (i & 511) * 4;
+    if (b >= nb) return;
+    float4 acc = init ? *reinterpret_cast<const float4 *>(init + (size_t)b * HID + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < TOPK; k++) {
+        int a = tp[b * TOPK + k]; float w = uw[a];
+        float4 d = *reinterpret_cast<const float4 *>(down + (size_t)a * HID + c);
+        acc.x = __fmaf_rn(w, d.x, acc.x); acc.y = __fmaf_rn(w, d.y, acc.y); acc.z = __fmaf_rn(w, d.z, acc.z); acc.w = __fmaf_rn(w, d.w, acc.w);
+    }
+    *reinterpret_cast<float4 *>(out + (size_t)b * HID + c) = acc;
+}
+extern "C" void k_combine(cudaStream_t st, const float *down, const float *uw, const int *tp, const float *init, float *out, int nb) {
+    if (nb <= 0) return;
+    combine_kernel<<<(nb * 512 + 255) / 256, 256, 0, st>>>(down, uw, tp, init, out, nb); g_launches++;
+}

@@ -1,0 +1,56 @@
+/* kernels.h -- launchers of the CUDA kernels, callable from C (gpre_api.c).  Every launcher enqueues on the given
+ * stream and returns; none allocates or synchronises. */
+#ifndef MAPLE_KERNELS_H
+#define MAPLE_KERNELS_H
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* where one expert's six arrays live in HBM (built from the reference's GLOC/GREG tables, maple.c:1106-1131) */
+typedef struct { const uint8_t *gc, *uc, *dc; const float *gs, *us, *ds; } ExpertPtrs;
+/* one unit of grouped-GEMM work: used expert u, first pair p0, cnt pairs (gpu_pre.m:329-333 uses the same triple) */
+typedef struct { int u, p0, cnt, pad; } MoeTile;
+
+typedef struct {
+    const ExpertPtrs *tab;   /* indexed by ue[u] when ue != NULL, else by u */
+    const int *ue;
+    const MoeTile *tiles; const int *ntiles; int max_tiles;
+    const int *ptok;         /* [np] token of each pair */
+    /* gate+up inputs */
+    const int8_t *hq; const float *hqs; const int *hqsum;          /* per token */
+    float *act;              /* [np][512] */
+    /* down inputs */
+    const int8_t *aq; const float *aqs; const int *aqsum;          /* per pair */
+    float *down;             /* [np][2048] */
+    /* optional stage outputs (NULL = off) */
+    float *gate, *up; int32_t *gu_dots, *dn_dots;
+} ExpertArgs;
+
+void k_count_reset(void); long k_count(void);
+
+void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb);
+void k_router_logits(cudaStream_t st, const uint16_t *router, const float *hn, const float *bias, float *logits, int nb);
+void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb);
+typedef struct {
+    const int *top; const float *topw; int nb;
+    unsigned *mask;          /* [256][mask_words] */
+    int mask_words;
+    int *nu, *ue, *estart, *ustart, *utok, *slot, *tp; float *uw;
+    MoeTile *tiles_a, *tiles_b; int *ntiles_a, *ntiles_b; int tn_a, tn_b;   /* two tile lists: sizes tn_a and tn_b */
+} GroupArgs;
+void k_group(cudaStream_t st, const GroupArgs *g);
+void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max);
+void k_combine(cudaStream_t st, const float *down, const float *uw, const int *tp, const float *init, float *out, int nb);
+
+/* register-decode + mma.sync grouped kernels (any token count; the decode-batch path); tn = 8 or 32 */
+void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
+void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
+
+void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
