@@ -1,0 +1,288 @@
+#!/usr/bin/env python3
+"""bench.py -- Maple MoE prefill throughput on B200: a 24-layer stack of mixture-of-experts blocks
+(d=2048, 256 ternary experts 512/2048, top-8) over 2048-token chunks of synthetic hidden states.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one 2048-token chunk through all 24 layers on each GPU.  `value` is tokens/s with the chunk already in
+HBM (device-timed, max over ranks); `e2e` is the same through the host-buffer entry point gmoe_forward (pinned host
+input copied in, result copied out, inside the timed region).  `roofline` describes the dominant kernel (the grouped
+gate+up GEMM) from CUDA events recorded around its launches during the timed region.  `cpu_baseline` times the
+reference's own CPU code (oracle/_ref, built from maple.c) on a bounded sample on this host.  `decode` repeats the
+measurement for the 64-conversation decode shape (HBM-bound).  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 20261125
+NB, LAYERS, H = 2048, 24, 2048
+EXPERT_BYTES = 798720
+OPS_PER_PAIR = 2 * (2 * 512 * 2048 + 2048 * 512)        # int8 multiply-adds x2 of one (token, expert) pair: 6,291,456
+GU_OPS_PER_PAIR = 2 * 2 * 512 * 2048                     # the gate+up share: 4,194,304
+METRIC, UNIT = "moe_prefill_tokens_per_s_2048tok_chunk_24_layers", "tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], False
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def summary(self):
+        self.stop_flag = True
+        self.join(timeout=6)
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": float(self.rows[0][1]) if self.rows else None,
+                "reasons": sorted(reasons), "samples": len(self.rows)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def init_dist(world):
+    if world == 1:
+        return None
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo")   # plumbing only: barrier and max over ranks of device-measured times
+    return dist
+
+
+def allmax(dist, v):
+    if dist is None:
+        return v
+    import torch
+    t = torch.tensor([v], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def barrier(dist):
+    if dist is not None:
+        dist.barrier()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def cpu_reference_arm(steps, warmup, as_baseline=False, budget_s=25.0):
+    """The reference's CPU path (maple.c through oracle/_ref, documented -ffast-math build) on this host's cores.
+    A step = one 2048-token chunk through ONE of the 24 layers (a bounded sample); the 24-layer figure scales it."""
+    from maple_runtime_b200 import lib as ml
+    from oracle import oracle as orc
+    clib = ml.load()
+    cores = os.cpu_count() or 1
+    kind = "reference" if orc.Reference.available(fast=True) else "port"
+    nlay = 2
+    layers = [(ml.synth_router(clib, SEED, L), ml.synth_norm(clib, SEED, L), ml.synth_experts(clib, SEED, L, 0, 256)) for L in range(nlay)]
+    x = ml.synth_hidden(clib, SEED, 1000, NB)
+    if kind == "reference":
+        ref = orc.Reference(fast=True)
+        threads = ref.threads(min(cores, 64))
+        for L in range(nlay):
+            ref.set_layer(L, *layers[L])
+        step = lambda i: ref.stack(x, i % nlay, 1)   # noqa: E731  seconds on the reference's own clock (maple.c:47)
+    else:
+        o = orc.Oracle(); threads = o.lib.orc_threads(min(cores, 64))
+
+        def step(i):
+            t = time.perf_counter(); o.moe(*layers[i % nlay], x, 1, dump=False); return time.perf_counter() - t
+    t_all = []
+    for i in range(warmup if not as_baseline else 1):
+        step(i)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        t_all.append(step(i))
+        if as_baseline and time.perf_counter() - t0 > budget_s:
+            break
+    per_layer = sum(t_all) / len(t_all)
+    value = NB / (per_layer * LAYERS)
+    sample = f"{len(t_all)} steps of one 2048-token chunk through 1 of 24 layers each (router to combine), scaled x24"
+    return value, per_layer, {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
+
+
+def reference_main(args, rank, world):
+    if rank != 0:
+        return
+    value, per_layer, cb = cpu_reference_arm(args.steps, args.warmup)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_layer * LAYERS * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic", "config": workload_config(1), "cpu_baseline": cb,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def workload_config(world):
+    return {"workload": "24-layer Maple MoE stack (d=2048, 256 ternary experts 512/2048, top-8), prefill chunk of 2048 tokens per GPU, "
+                        "hidden ~N(0,1), random router (near-uniform routing), seeded synthetic weights",
+            "tokens_per_step_per_gpu": NB, "layers": LAYERS, "parallelism": "replicas" if world > 1 else "single",
+            "l2": "inputs larger than L2: 4.9 GB of expert weights are streamed from HBM every step"}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for small profiling captures (not a bench number)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true")
+    args = ap.parse_args()
+    rank, local, world = dist_env()
+    if args.impl == "reference":
+        return reference_main(args, rank, world)
+    warm = max(args.warmup, 3)
+    dist = init_dist(world)
+
+    from maple_runtime_b200 import lib as ml
+    g = ml.Gpre(NB, device=local)
+    clib = g.lib
+    nl = args.layers
+    for L in range(nl):
+        g.synth_layer(SEED, L)
+    nring = 4
+    ring = np.concatenate([ml.synth_hidden(clib, SEED, 2000 + rank * 16 + c, NB) for c in range(nring)])
+    g._chk(clib.gmoe_chunks_upload(ring.ctypes.data, NB, nring))
+
+    # ---- value: chunk resident in HBM, K steps between two synchronisations, device-timed ----
+    import ctypes as C
+    ev_total = []
+    for i in range(warm):
+        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None)); g._chk(clib.gmoe_sync())
+    sampler = ClockSampler(local); sampler.start()
+    g.profile(1 << 4)                                  # events around the gate+up launches only
+    l0 = clib.gmoe_launch_count()
+    barrier(dist)
+    t_dev = 0.0
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None))
+        t_dev += g._chk(clib.gmoe_sync())              # device seconds of this step (events on the library's stream)
+    wall = time.perf_counter() - wall0
+    barrier(dist)
+    launches = clib.gmoe_launch_count() - l0
+    secs, nlaunch = g.profile_read()
+    g.profile(0)
+    clocks = sampler.summary()
+    t_dev = allmax(dist, t_dev)
+    value = world * NB * args.steps / t_dev
+
+    # ---- stage breakdown (separate pass, all stages timed) ----
+    g.profile(0xFF)
+    for i in range(2):
+        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None))
+    st_secs, st_n = g.profile_read()
+    g.profile(0)
+    breakdown = {name: round(float(s) / (2 * nl) * 1e6, 2) for name, s in zip(g.STAGES, st_secs)}   # us per layer
+
+    # ---- e2e: host buffers through gmoe_forward, copies inside the timed region ----
+    hx = clib.gmoe_pinned_alloc(NB * H * 4)
+    hbuf = np.ctypeslib.as_array(C.cast(hx, C.POINTER(C.c_float)), shape=(NB, H))
+    t_e2e = 0.0
+    for i in range(warm + args.steps):
+        hbuf[:] = ring[(i % nring) * NB:(i % nring + 1) * NB]
+        if i == warm:
+            barrier(dist)
+        t = g._chk(clib.gmoe_forward(hx, NB, 0, nl, None))
+        if i >= warm:
+            t_e2e += t
+    barrier(dist)
+    t_e2e = allmax(dist, t_e2e)
+    e2e = world * NB * args.steps / t_e2e
+
+    # ---- roofline of the dominant kernel ----
+    pk = peaks()
+    gu_t = float(secs[4]) / max(int(nlaunch[4]), 1)
+    gu_tops = GU_OPS_PER_PAIR * NB * 8 / gu_t / 1e12
+    int8_peak = 2.0 * pk["bf16_tflops_sustained"]
+    roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary)", "bound": "tensor", "achieved": gu_tops, "peak": int8_peak, "unit": "TOP/s (int8)",
+                "frac": gu_tops / int8_peak, "traffic": None, "launches_timed": int(nlaunch[4]), "avg_launch_us": gu_t * 1e6,
+                "peak_note": f"2 x the {pk['src']} sustained bf16 figure ({pk['bf16_tflops_sustained']} TF/s): no int8 figure is measured on this pool",
+                "weights_gbs": NB and 256 * 2 * 264192 / gu_t / 1e9}
+
+    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+           "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+           "data": "synthetic", "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
+           "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": NB * H * 4, "d2h_bytes_per_step": NB * H * 4},
+           "roofline": roofline, "stage_us_per_layer": breakdown, "wall_s_timed_region": wall,
+           "whole_path_int8_tops": OPS_PER_PAIR * NB * 8 * nl * args.steps / t_dev / 1e12}
+    if nl != LAYERS:
+        out["config"]["layers"] = nl
+        out["note"] = "reduced layer count: a profiling run, not a benchmark number"
+
+    # ---- decode shape: 64 conversations x 1 token, one layer at a time over all layers (HBM-bound) ----
+    if not args.no_decode and rank == 0:
+        out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
+    if not args.no_cpu and rank == 0 and world >= 1:
+        _, _, out["cpu_baseline"] = cpu_reference_arm(8, 1, as_baseline=True)
+    if rank == 0:
+        print(json.dumps(out))
+
+
+def decode_leg(g, clib, ml, nl, pk, warm, steps):
+    """64 conversations x 1 token through all layers (the --multi 64 shape, maple.c:1189-1199): weight-bandwidth bound."""
+    nb = 64
+    x = ml.synth_hidden(clib, SEED, 3000, nb)
+    g._chk(clib.gmoe_chunks_upload(x.ctypes.data, nb, 1))
+    for _ in range(warm):
+        g._chk(clib.gmoe_forward_chunk(0, nb, 0, nl, None)); g._chk(clib.gmoe_sync())
+    g.profile(0xFF)
+    t = 0.0
+    for _ in range(steps):
+        g._chk(clib.gmoe_forward_chunk(0, nb, 0, nl, None)); t += g._chk(clib.gmoe_sync())
+    secs, n = g.profile_read(); g.profile(0)
+    nu = int(g.peek("nu", nb)[0])                      # used experts of the last layer (others are alike)
+    layer_bytes = nu * EXPERT_BYTES + 256 * 2048 * 2 + nb * 2048 * 4 * 3
+    gu_bytes = nu * 2 * 264192
+    gu_t = float(secs[4]) / max(int(n[4]), 1)
+    per_layer = t / steps / nl
+    return {"metric": "moe_decode_tokens_per_s_64_conversations", "value": nb * steps / t, "unit": UNIT,
+            "ms_per_step": t / steps * 1e3, "used_experts": nu, "bytes_per_layer": layer_bytes,
+            "roofline": {"kernel": "gate+up weight stream (register-decode mma.sync)", "bound": "hbm", "achieved": gu_bytes / gu_t / 1e9,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_bytes / gu_t / 1e9 / pk["hbm_gbs"], "traffic": None,
+                         "avg_launch_us": gu_t * 1e6},
+            "layer_hbm_frac": layer_bytes / per_layer / 1e9 / pk["hbm_gbs"],
+            "stage_us_per_layer": {name: round(float(s) / (steps * nl) * 1e6, 2) for name, s in zip(g.STAGES, secs)}}
+
+
+if __name__ == "__main__":
+    main()

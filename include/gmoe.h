@@ -40,12 +40,18 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne);
 double gmoe_moe(int L, const float *x, int nb, float *y, const float *bias);
 
 /* ---- the residual stream through nl layers starting at l0 ----------------------------------------------------- */
-/* Host in/out: per layer hn = rmsnorm(x, post_ln), x += moe(hn) (maple.c:733-834).  Returns GPU seconds. */
+/* Host in/out: per layer hn = rmsnorm(x, post_ln), x += moe(hn) (maple.c:733-834).  Returns the seconds on the
+ * device timeline from the start of the host-to-device copy of x to the end of the copy back. */
 double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias);
 /* Device-resident form: upload once, run (asynchronous, on the library's stream), download. */
 int gmoe_x_upload(const float *x, int nb);
 int gmoe_x_download(float *x, int nb);
 int gmoe_forward_dev(int nb, int l0, int nl, const float *bias);
+/* A ring of input chunks kept in HBM so a benchmark step starts with its input resident: chunk c of nchunks, each
+ * nb tokens.  gmoe_forward_chunk copies chunk c into the hidden state (device to device) and runs the layers,
+ * asynchronously like gmoe_forward_dev. */
+int gmoe_chunks_upload(const float *x, int nb, int nchunks);
+int gmoe_forward_chunk(int chunk, int nb, int l0, int nl, const float *bias);
 /* Waits for the stream; returns the GPU seconds between the last gmoe_forward_dev's first and last kernel. */
 double gmoe_sync(void);
 /* rmsnorm(post_ln[L]) of the device-resident hidden state + int8 + router logits: the part of gfull_attn
@@ -68,6 +74,14 @@ int gmoe_set_path(int path);
  * numbered in registration order) back to the host, to check what lives in HBM. */
 int gmoe_region_read(int region, size_t off, void *dst, size_t bytes);
 int gmoe_region_count(void);
+
+/* ---- per-stage timing (the reference's GPRE_PROF=1 split, gpu_pre.m:349-365) ------------------------------------ */
+/* mask: bit s set = CUDA events are recorded around stage s of every layer (0 norm+int8, 1 router, 2 top-8, 3 grouping,
+ * 4 gate+up, 5 SiLU int8, 6 down, 7 combine).  gmoe_profile_read waits for the stream, adds up the recorded intervals
+ * into secs[8] / launches[8] (kernel launches timed) and clears them. */
+#define GMOE_STAGES 8
+int gmoe_profile(unsigned mask);
+int gmoe_profile_read(double *secs, long *launches);
 
 /* ---- utilities -------------------------------------------------------------------------------------------------- */
 const char *gmoe_last_error(void);

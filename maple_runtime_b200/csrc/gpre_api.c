@@ -48,6 +48,8 @@ static struct {
     ExpertPtrs *tab_call;      /* the used experts of one gpre_moe call */
     MoeTile *h_tiles; ExpertPtrs *h_tab;   /* host staging for the reference-shaped calls */
     double t_experts;          /* GPU seconds in gfull_moe, reported by gfull_report */
+    float *ring; int ring_nb, ring_n;
+    unsigned prof_mask; cudaEvent_t *pev; int pev_n, pev_cap; unsigned char *pev_stage; long *pev_launch;
     int fwd_timed;
 } S;
 
@@ -194,6 +196,38 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     l->set = 1; return 0;
 }
 
+/* ---- per-stage events ------------------------------------------------------------------------------------------ */
+static long g_before;
+static void prof_begin(int stage) {
+    if (!(S.prof_mask >> stage & 1u)) return;
+    if (S.pev_n + 2 > S.pev_cap) {
+        int cap = S.pev_cap ? S.pev_cap * 2 : 1024;
+        cudaEvent_t *ev = realloc(S.pev, (size_t)cap * sizeof *ev);
+        unsigned char *st = realloc(S.pev_stage, (size_t)cap); long *ln = realloc(S.pev_launch, (size_t)cap * sizeof *ln);
+        if (!ev || !st || !ln) return;
+        for (int i = S.pev_cap; i < cap; i++) cudaEventCreate(&ev[i]);
+        S.pev = ev; S.pev_stage = st; S.pev_launch = ln; S.pev_cap = cap;
+    }
+    g_before = k_count();
+    cudaEventRecord(S.pev[S.pev_n], S.st);
+}
+static void prof_end(int stage) {
+    if (!(S.prof_mask >> stage & 1u) || S.pev_n + 2 > S.pev_cap) return;
+    cudaEventRecord(S.pev[S.pev_n + 1], S.st);
+    S.pev_stage[S.pev_n] = (unsigned char)stage; S.pev_launch[S.pev_n] = k_count() - g_before; S.pev_n += 2;
+}
+int gmoe_profile(unsigned mask) { if (!S.ready) return fail("gmoe", "not initialised"); S.prof_mask = mask; return 0; }
+int gmoe_profile_read(double *secs, long *launches) {
+    if (!S.ready) return fail("gmoe", "not initialised");
+    CU("gmoe", cudaStreamSynchronize(S.st));
+    for (int s = 0; s < GMOE_STAGES; s++) { secs[s] = 0; launches[s] = 0; }
+    for (int i = 0; i < S.pev_n; i += 2) {
+        float ms = 0; cudaEventElapsedTime(&ms, S.pev[i], S.pev[i + 1]);
+        secs[S.pev_stage[i]] += ms * 1e-3; launches[S.pev_stage[i]] += S.pev_launch[i];
+    }
+    S.pev_n = 0; return 0;
+}
+
 /* ---- the stages ------------------------------------------------------------------------------------------------ */
 static int tile_tn(int nb) { return nb <= 256 ? 8 : 32; }
 
@@ -213,19 +247,21 @@ static void run_group(int nb) {
 static void run_experts(const ExpertPtrs *tab, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
     ExpertArgs a; fill_expert_args(&a, tab, ue, nb);
     int tn = tile_tn(nb);
-    if (which & 1) k_gateup_mma(S.st, &a, tn);
-    if (which & 2) k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK);
-    if (which & 4) k_down_mma(S.st, &a, tn);
+    if (which & 1) { prof_begin(4); k_gateup_mma(S.st, &a, tn); prof_end(4); }
+    if (which & 2) { prof_begin(5); k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK); prof_end(5); }
+    if (which & 4) { prof_begin(6); k_down_mma(S.st, &a, tn); prof_end(6); }
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {
     LayerDev *l = &S.ly[L];
-    k_norm_prep(S.st, norm ? S.x : S.hn, norm ? l->post_ln : NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
-    k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb);
-    k_topk(S.st, S.logits, S.top, S.topw, nb);
-    run_group(nb);
+    prof_begin(0); k_norm_prep(S.st, norm ? S.x : S.hn, norm ? l->post_ln : NULL, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
+    prof_begin(1); k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb); prof_end(1);
+    prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    prof_begin(3); run_group(nb); prof_end(3);
     run_experts(l->tab, S.ue, nb, 7);
+    prof_begin(7);
     if (norm) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb); else k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
+    prof_end(7);
 }
 static int check_call(const char *who, int L, int nb) {
     if (!S.ready) return fail(who, "not initialised");
@@ -266,6 +302,24 @@ int gmoe_forward_dev(int nb, int l0, int nl, const float *bias) {
     S.nb_cur = nb;
     return 0;
 }
+int gmoe_chunks_upload(const float *x, int nb, int nchunks) {
+    if (!S.ready || nb < 1 || nb > S.maxtok || nchunks < 1) return fail("gmoe", "ring of %d chunks of %d tokens", nchunks, nb);
+    if (S.ring) { cudaFree(S.ring); S.ring = NULL; }
+    size_t bytes = (size_t)nchunks * nb * HID * 4;
+    if (cudaMalloc((void **)&S.ring, bytes) != cudaSuccess) return fail("gmoe", "no device memory for %d chunks", nchunks);
+    CU("gmoe", cudaMemcpyAsync(S.ring, x, bytes, cudaMemcpyHostToDevice, S.st)); CU("gmoe", cudaStreamSynchronize(S.st));
+    S.ring_nb = nb; S.ring_n = nchunks; return 0;
+}
+int gmoe_forward_chunk(int chunk, int nb, int l0, int nl, const float *bias) {
+    if (!S.ring || nb != S.ring_nb || chunk < 0 || chunk >= S.ring_n) return fail("gmoe", "chunk %d of %d tokens is not in the ring", chunk, nb);
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1;
+    const float *bd = bias_dev(bias);
+    cudaEventRecord(S.e0, S.st);
+    cudaMemcpyAsync(S.x, S.ring + (size_t)chunk * nb * HID, (size_t)nb * HID * 4, cudaMemcpyDeviceToDevice, S.st);
+    for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+    cudaEventRecord(S.e1, S.st);
+    S.nb_cur = nb; return 0;
+}
 double gmoe_sync(void) { if (!S.ready) { fail("gmoe", "not initialised"); return -1.0; } return finish("gmoe"); }
 int gmoe_x_upload(const float *x, int nb) {
     if (!S.ready || nb < 1 || nb > S.maxtok) return fail("gmoe", "upload of %d tokens", nb);
@@ -276,10 +330,15 @@ int gmoe_x_download(float *x, int nb) {
     CU("gmoe", cudaMemcpyAsync(x, S.x, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st)); return 0;
 }
-double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias) {
-    if (gmoe_x_upload(x, nb)) return -1.0;
-    if (gmoe_forward_dev(nb, l0, nl, bias)) return -1.0;
+double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias) {   /* the seconds include both copies */
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1.0;
+    const float *bd = bias_dev(bias);
+    cudaEventRecord(S.e0, S.st);
+    CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
+    for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
     CUD("gmoe", cudaMemcpyAsync(x, S.x, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
+    cudaEventRecord(S.e1, S.st);
+    S.nb_cur = nb;
     return finish("gmoe");
 }
 int gmoe_post_norm(int L, int nb, float *logits) {

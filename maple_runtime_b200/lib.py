@@ -37,7 +37,9 @@ DECLS = {
     "gmoe_set_layer": (i32, [i32, vp, vp, vp, vp]), "gmoe_synth_layer": (i32, [u64, i32, i32, i32]),
     "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]),
     "gmoe_x_upload": (i32, [vp, i32]), "gmoe_x_download": (i32, [vp, i32]),
-    "gmoe_forward_dev": (i32, [i32, i32, i32, vp]), "gmoe_sync": (f64, []), "gmoe_post_norm": (i32, [i32, i32, vp]),
+    "gmoe_forward_dev": (i32, [i32, i32, i32, vp]),
+    "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),
+    "gmoe_profile": (i32, [C.c_uint]), "gmoe_profile_read": (i32, [vp, vp]), "gmoe_sync": (f64, []), "gmoe_post_norm": (i32, [i32, i32, vp]),
     "gmoe_peek": (i32, [C.c_char_p, vp, sz]), "gmoe_poke": (i32, [C.c_char_p, vp, sz]),
     "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]),
     "gmoe_region_read": (i32, [i32, sz, vp, sz]), "gmoe_region_count": (i32, []),
@@ -93,6 +95,7 @@ class Gpre:
             self._chk(self.lib.gmoe_set_device(device))
         self._chk(self.lib.gmoe_init(maxtok))
         self.maxtok = maxtok
+        self.layer_region = {}
 
     def err(self):
         return (self.lib.gmoe_last_error() or b"").decode()
@@ -105,6 +108,17 @@ class Gpre:
     # --- weights
     def synth_layer(self, seed, L, e0=0, ne=256):
         self._chk(self.lib.gmoe_synth_layer(seed, L, e0, ne))
+        self.layer_region[L] = self.lib.gmoe_region_count() - 1
+
+    STAGES = ("norm_int8", "router", "top8", "grouping", "gate_up", "silu_int8", "down", "combine")
+
+    def profile(self, mask):
+        self._chk(self.lib.gmoe_profile(mask))
+
+    def profile_read(self):
+        secs = np.zeros(8, np.float64); n = np.zeros(8, np.int64)
+        self._chk(self.lib.gmoe_profile_read(_p(secs), _p(n)))
+        return secs, n
 
     def region(self, buf):
         """buf: page-aligned uint8 array whose length is a multiple of the page size."""
