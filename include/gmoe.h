@@ -75,6 +75,24 @@ int gmoe_set_path(int path);
 int gmoe_region_read(int region, size_t off, void *dst, size_t bytes);
 int gmoe_region_count(void);
 
+/* ---- grouping without any allocation ------------------------------------------------------------------------------ */
+/* No counterpart in the reference (its grouping is host code, maple.c:924-938); added for callers that cannot
+ * allocate device memory when they need the grouping: a server working inside a memory budget fixed at start-up, a
+ * plug-in inside another runtime's pool, a latency path where cudaMalloc's device-wide synchronisation is not
+ * acceptable.  Same result as the grouping stage of gmoe_moe (NU, UE, USTART, UTOK, UW, tp of maple.c:924-938,
+ * 1018-1019), computed with scratch that is a fixed array inside the loaded library (about 205 KB per GPU, held until
+ * the process exits) instead of buffers from cudaMalloc.  All pointers are DEVICE pointers owned by the caller:
+ *   top [nb][8] expert ids, topw [nb][8] routing weights  ->  nu [1], ue [256], ustart [257], utok [nb*8], uw [nb*8],
+ *   tp [nb*8].  stream: a cudaStream_t (NULL = the default stream); the work is queued there, not waited for.
+ * Limit: 1 <= nb <= GMOE_NOALLOC_MAXTOK; more is rejected with -2 and a message.  Returns 0, -1 (null pointer),
+ * -2 (too many tokens), -3 (CUDA error), each with a "gmoe: ..." line on stderr.
+ * The first call on a GPU looks up the array's device address (cudaGetSymbolAddress); make that first call before
+ * any stream capture starts.  The array is shared by every call and keeps the previous call's contents; the masks
+ * are cleared at the start of each call.  Calls that overlap on the GPU race on it: order them. */
+#define GMOE_NOALLOC_MAXTOK 2048
+int gmoe_group_noalloc(const int *top, const float *topw, int nb, int *nu, int *ue, int *ustart, int *utok, float *uw,
+                       int *tp, void *stream);
+
 /* ---- per-stage timing (the reference's GPRE_PROF=1 split, gpu_pre.m:349-365) ------------------------------------ */
 /* mask: bit s set = CUDA events are recorded around stage s of every layer (0 norm+int8, 1 router, 2 top-8, 3 grouping,
  * 4 gate+up, 5 SiLU int8, 6 down, 7 combine).  gmoe_profile_read waits for the stream, adds up the recorded intervals
