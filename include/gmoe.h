@@ -101,6 +101,12 @@ int gmoe_group_noalloc(const int *top, const float *topw, int nb, int *nu, int *
 int gmoe_profile(unsigned mask);
 int gmoe_profile_read(double *secs, long *launches);
 
+/* ---- check of the tensor-core building blocks ------------------------------------------------------------------------ */
+/* d[128][n] = a[128][k] (unsigned bytes) x b[n][k]^T (signed bytes), k = 128*kblocks, on one CTA with tcgen05.mma
+ * kind::i8; mode 0 stages A in shared memory, mode 1 writes A to tensor memory.  Host pointers.  0 = ran,
+ * -1 = bad arguments or CUDA error, -2 = the MMA never signalled completion. */
+int gmoe_umma_selftest(const uint8_t *a, const int8_t *b, int n, int kblocks, int mode, int32_t *d);
+
 /* ---- utilities -------------------------------------------------------------------------------------------------- */
 const char *gmoe_last_error(void);
 long gmoe_launch_count(void);             /* kernels launched by this library since load */

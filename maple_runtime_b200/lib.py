@@ -43,6 +43,7 @@ DECLS = {
     "gmoe_peek": (i32, [C.c_char_p, vp, sz]), "gmoe_poke": (i32, [C.c_char_p, vp, sz]),
     "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]),
     "gmoe_group_noalloc": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
+    "gmoe_umma_selftest": (i32, [vp, vp, i32, i32, i32, vp]),
     "gmoe_region_read": (i32, [i32, sz, vp, sz]), "gmoe_region_count": (i32, []),
     "gmoe_last_error": (C.c_char_p, []), "gmoe_launch_count": (C.c_long, []),
     "gmoe_pinned_alloc": (vp, [sz]), "gmoe_pinned_free": (None, [vp]), "gmoe_device_info": (i32, [vp, i32, vp, vp]),
