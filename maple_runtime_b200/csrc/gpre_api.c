@@ -43,7 +43,7 @@ static struct {
     float *x, *hn, *y, *hqs, *logits, *topw, *uw, *act, *aqs, *down, *gate, *up, *bias;
     int8_t *hq, *aq;
     int *hqsum, *top, *nu, *ue, *estart, *ustart, *utok, *slot, *tp, *aqsum, *ntiles_a, *ntiles_b, *gu_dots, *dn_dots;
-    unsigned *mask;
+    unsigned *mask; int *err, *h_err;
     MoeTile *tiles_a, *tiles_b;
     ExpertPtrs *tab_call;      /* the used experts of one gpre_moe call */
     MoeTile *h_tiles; ExpertPtrs *h_tab;   /* host staging for the reference-shaped calls */
@@ -79,8 +79,10 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);
     ALLOC(act, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
-    ALLOC(tab_call, NEXP * sizeof(ExpertPtrs));
-    S.h_tiles = malloc((P / 8 + NEXP) * sizeof(MoeTile)); S.h_tab = malloc(NEXP * sizeof(ExpertPtrs));
+    ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16);
+    CU(who, cudaMemset(S.err, 0, 16));
+    CU(who, cudaHostAlloc((void **)&S.h_err, 16, cudaHostAllocDefault)); *S.h_err = 0;
+    S.h_tiles = malloc(2 * (P / 8 + NEXP) * sizeof(MoeTile)); S.h_tab = malloc(NEXP * sizeof(ExpertPtrs));
     if (!S.h_tiles || !S.h_tab) return fail(who, "out of host memory");
     S.ready = 1;
     fprintf(stderr, "%s: %s, chunks up to %d tokens, %.0f MB of device workspace, weights resident in HBM\n", who, pr.name, maxtok,
@@ -231,10 +233,12 @@ int gmoe_profile_read(double *secs, long *launches) {
 /* ---- the stages ------------------------------------------------------------------------------------------------ */
 static int tile_tn(int nb) { return nb <= 256 ? 8 : 32; }
 
+static int use_umma(int nb) { return S.path == 2 || (S.path == 0 && nb >= 512); }
 static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const int *ue, int nb) {
     memset(a, 0, sizeof *a);
-    a->tab = tab; a->ue = ue; a->tiles = S.tiles_a; a->ntiles = S.ntiles_a;
-    a->max_tiles = nb * TOPK / tile_tn(nb) + NEXP; a->ptok = S.utok;
+    a->tab = tab; a->ue = ue; a->ptok = S.utok; a->err = S.err;
+    if (use_umma(nb)) { a->tiles = S.tiles_b; a->ntiles = S.ntiles_b; a->max_tiles = nb * TOPK / 128 + NEXP; }
+    else { a->tiles = S.tiles_a; a->ntiles = S.ntiles_a; a->max_tiles = nb * TOPK / tile_tn(nb) + NEXP; }
     a->hq = S.hq; a->hqs = S.hqs; a->hqsum = S.hqsum; a->act = S.act;
     a->aq = S.aq; a->aqs = S.aqs; a->aqsum = S.aqsum; a->down = S.down;
     if (S.keep) { a->gate = S.gate; a->up = S.up; a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
@@ -247,9 +251,10 @@ static void run_group(int nb) {
 static void run_experts(const ExpertPtrs *tab, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
     ExpertArgs a; fill_expert_args(&a, tab, ue, nb);
     int tn = tile_tn(nb);
-    if (which & 1) { prof_begin(4); k_gateup_mma(S.st, &a, tn); prof_end(4); }
+    int um = use_umma(nb);
+    if (which & 1) { prof_begin(4); if (um) k_gateup_umma(S.st, &a); else k_gateup_mma(S.st, &a, tn); prof_end(4); }
     if (which & 2) { prof_begin(5); k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK); prof_end(5); }
-    if (which & 4) { prof_begin(6); k_down_mma(S.st, &a, tn); prof_end(6); }
+    if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a); else k_down_mma(S.st, &a, tn); prof_end(6); }
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {
@@ -275,7 +280,12 @@ static const float *bias_dev(const float *bias) {
     return S.bias;
 }
 static double finish(const char *who) {
+    cudaMemcpyAsync(S.h_err, S.err, 4, cudaMemcpyDeviceToHost, S.st);
     cudaError_t e = cudaStreamSynchronize(S.st);
+    if (e == cudaSuccess && *S.h_err) {
+        *S.h_err = 0; cudaMemsetAsync(S.err, 0, 4, S.st);
+        fail(who, "a kernel gave up waiting on a barrier (bounded wait ran out); results are invalid"); return -1.0;
+    }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { fail(who, "%s", cudaGetErrorString(e)); return -1.0; }
     float ms = 0; cudaEventElapsedTime(&ms, S.e0, S.e1);
@@ -360,12 +370,16 @@ static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc,
     int np = ustart[nu];
     if (np != nb * TOPK) return fail(who, "%d pairs for %d tokens (need %d per token)", np, nb, TOPK);
     if (ustart[0] != 0) return fail(who, "ustart[0] = %d", ustart[0]);
-    int tn = tile_tn(nb), nt = 0;
+    int tn = tile_tn(nb), nt = 0, ntb = 0;
+    MoeTile *h_tb = S.h_tiles + ((size_t)S.maxp / 8 + NEXP);
     for (int u = 0; u < nu; u++) {
         if (ustart[u + 1] <= ustart[u]) return fail(who, "used expert %d has no pairs", u);
         if (resolve(who, loc + u * 12, regs, &S.h_tab[u])) return -1;
         for (int p = ustart[u]; p < ustart[u + 1]; p += tn) {   /* gpu_pre.m:329-333 */
             MoeTile m = {u, p, ustart[u + 1] - p < tn ? ustart[u + 1] - p : tn, 0}; S.h_tiles[nt++] = m;
+        }
+        for (int p = ustart[u]; p < ustart[u + 1]; p += 128) {
+            MoeTile m = {u, p, ustart[u + 1] - p < 128 ? ustart[u + 1] - p : 128, 0}; h_tb[ntb++] = m;
         }
     }
     for (int a = 0; a < np; a++) if (ptok[a] < 0 || ptok[a] >= nb) return fail(who, "ptok[%d] = %d", a, ptok[a]);
@@ -373,6 +387,8 @@ static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc,
     CU(who, cudaMemcpyAsync(S.tab_call, S.h_tab, (size_t)nu * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.ntiles_a, &nt, 4, cudaMemcpyHostToDevice, S.st));
+    CU(who, cudaMemcpyAsync(S.tiles_b, h_tb, (size_t)ntb * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
+    CU(who, cudaMemcpyAsync(S.ntiles_b, &ntb, 4, cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.ustart, ustart, (size_t)(nu + 1) * 4, cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.nu, &nu, 4, cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.utok, ptok, (size_t)np * 4, cudaMemcpyHostToDevice, S.st));
@@ -456,6 +472,7 @@ int gmoe_poke(const char *name, const void *src, size_t bytes) {
 int gmoe_stage(const char *name, int L, int nb) {
     if (check_call("gmoe", L, nb)) return -1;
     LayerDev *l = &S.ly[L];
+    cudaEventRecord(S.e0, S.st);
     if (!strcmp(name, "norm")) k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb);
     else if (!strcmp(name, "prep")) k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
     else if (!strcmp(name, "router")) k_router_logits(S.st, l->router, S.hn, NULL, S.logits, nb);
@@ -468,10 +485,8 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "combine_y")) k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
     else if (!strcmp(name, "combine_x")) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
     else return fail("gmoe", "no stage named %s", name);
-    cudaError_t e = cudaStreamSynchronize(S.st);
-    if (e == cudaSuccess) e = cudaGetLastError();
-    if (e != cudaSuccess) return fail("gmoe", "stage %s: %s", name, cudaGetErrorString(e));
-    return 0;
+    cudaEventRecord(S.e1, S.st);
+    return finish("gmoe") < 0 ? -1 : 0;
 }
 
 int gmoe_region_count(void) { return S.nreg; }

@@ -26,6 +26,7 @@ typedef struct {
     float *down;             /* [np][2048] */
     /* optional stage outputs (NULL = off) */
     float *gate, *up; int32_t *gu_dots, *dn_dots;
+    int *err;                /* set to 1 by a kernel whose bounded wait ran out */
 } ExpertArgs;
 
 void k_count_reset(void); long k_count(void);
@@ -47,6 +48,10 @@ void k_combine(cudaStream_t st, const float *down, const float *uw, const int *t
 /* register-decode + mma.sync grouped kernels (any token count; the decode-batch path); tn = 8 or 32 */
 void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
+
+/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */
+void k_gateup_umma(cudaStream_t st, const ExpertArgs *a);
+void k_down_umma(cudaStream_t st, const ExpertArgs *a);
 
 void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
 

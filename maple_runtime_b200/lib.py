@@ -165,6 +165,10 @@ class Gpre:
         arr = np.ascontiguousarray(arr)
         self._chk(self.lib.gmoe_poke(name.encode(), _p(arr), arr.nbytes))
 
+    def set_path(self, path):
+        """0 = by size, 1 = register-decode mma.sync kernels, 2 = tcgen05 kernels."""
+        self._chk(self.lib.gmoe_set_path(path))
+
     def keep_stages(self, keep=True):
         self._chk(self.lib.gmoe_keep_stages(int(keep)))
 

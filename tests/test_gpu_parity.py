@@ -100,6 +100,30 @@ def test_fixtures_from_the_reference(case, layers, clib):
     assert np.array_equal(digest(y), GOLD[f"{case}/y_sha"])
 
 
+@pytest.mark.parametrize("nb,stream,norm,zipf", [(1, 401, 0, False), (5, 402, 1, False), (33, 403, 0, False), (128, 404, 1, False),
+                                                  (300, 405, 1, True), (600, 406, 1, False)])
+def test_tcgen05_path_all_stages_equal_oracle(nb, stream, norm, zipf, layers, clib, oracle, weights):
+    """The tensor-core (tcgen05 kind::i8) grouped kernels forced for every size, including one-token tiles, tiles
+    padded to 16 columns, experts split over several 128-token tiles (Zipf bias) and the size where it is the default."""
+    from maple_runtime_b200 import lib as ml
+    g = layers
+    bias = ml.synth_zipf_bias(clib, SEED) if zipf else None
+    x = weights.hidden(stream, nb)
+    want, d = oracle.moe(*weights.layer(1), x, norm, bias, dots=True)
+    g.set_path(2)
+    try:
+        if norm:
+            got = x.copy(); g.forward(got, 1, 1, bias)
+        else:
+            got, _ = g.moe(1, x, bias)
+        check_stages(g, nb, d)
+    finally:
+        g.set_path(0)
+    if zipf:
+        assert np.diff(d["ustart"][:int(d["nu"][0]) + 1]).max() > 128
+    assert same_bits(got, want), f"rel {rel(got, want):.3e}"
+
+
 def test_gpre_moe_reference_signature(layers, clib, oracle, weights):
     """The drop-in call of maple.c:763: weights registered as page-aligned host regions, grouping from the host."""
     from maple_runtime_b200 import lib as ml
