@@ -21,6 +21,7 @@
 // Tensor memory (512 columns): [0,128) accumulator 0, [128,256) accumulator 1, [256,512) four A stages of 2 x 32 columns.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "kernels.h"
 #include "dev_math.cuh"
 #include "umma.cuh"
@@ -91,6 +92,7 @@ __global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
                 const int kb = sb * 4 + q, s = kb % UM_STAGES, it = kb / UM_STAGES;
                 if (!mbar_wait(&sh->empty[s], (it & 1) ^ 1, abortp)) { live = false; break; }
                 tc_fence_after();
+                if (a.dbg & 2) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->a_full[s]); continue; }
                 const uint32_t w[8] = {cur[2 * q].x, cur[2 * q].y, cur[2 * q].z, cur[2 * q].w, cur[2 * q + 1].x, cur[2 * q + 1].y, cur[2 * q + 1].z, cur[2 * q + 1].w};
                 uint32_t r[32];
 #pragma unroll
@@ -105,7 +107,7 @@ __global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
             }
         }
         // ---------------- epilogue: lane = weight row, columns = tokens ----------------
-        if (live && mbar_wait(&sh->acc_full, 0, abortp)) {
+        if (live && mbar_wait(&sh->acc_full, 0, abortp) && !(a.dbg & 8)) {
             tc_fence_after();
             const uint32_t d_lane = tb + ((uint32_t)((warp & 3) * 32) << 16);
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
                 if (!mbar_wait(&sh->empty[s], (it & 1) ^ 1, abortp)) live = false;
                 else {
                     const uint32_t dst = smem_u32(bs + s * UM_BSTAGE);
-                    for (int i = lane; i < cnt * 8; i += 32) {
+                    for (int i = lane; i < cnt * 8 && !(a.dbg & 1); i += 32) {
                         const int n = i >> 3, c = i & 7;
                         cp_async16(dst + n * 128 + ((c ^ (n & 7)) << 4), src + (size_t)sh->tok[n] * KBYTES + kb * 128 + c * 16);
                     }
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
             tc_fence_after();
             const uint32_t bbase = smem_u32(bs + s * UM_BSTAGE);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
+            for (int k = 0; k < 4 && !(a.dbg & 4); k++) {
                 const uint64_t bd = smem_desc_k128(bbase, k * 32);
                 umma_i8_ts(tb, tb + 256 + s * 64 + k * 8, bd, idesc, (kb | k) != 0);
                 umma_i8_ts(tb + 128, tb + 256 + s * 64 + 32 + k * 8, bd, idesc, (kb | k) != 0);
@@ -193,7 +195,10 @@ static void launch(cudaStream_t st, const ExpertArgs *a) {
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(expert_umma_kernel<KB, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
     dim3 grid(GATEUP ? 4 : 8, a->max_tiles);
-    expert_umma_kernel<KB, GATEUP><<<grid, 320, smem, st>>>(*a);
+    ExpertArgs b = *a;
+    static int dbg = -1; if (dbg < 0) { const char *e = getenv("GMOE_UMMA_DBG"); dbg = e ? atoi(e) : 0; }
+    b.dbg = dbg;
+    expert_umma_kernel<KB, GATEUP><<<grid, 320, smem, st>>>(b);
     k_count_add(1);
 }
 extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a) { if (a->max_tiles > 0) launch<16, true>(st, a); }

@@ -27,6 +27,7 @@ typedef struct {
     /* optional stage outputs (NULL = off) */
     float *gate, *up; int32_t *gu_dots, *dn_dots;
     int *err;                /* set to 1 by a kernel whose bounded wait ran out */
+    int dbg;                 /* timing experiments only (GMOE_UMMA_DBG): bit 0 no B copies, 1 no A decode/store, 2 no MMA, 3 no epilogue */
 } ExpertArgs;
 
 void k_count_reset(void); long k_count(void);
