@@ -17,7 +17,8 @@ static __device__ const unsigned long long DEV_EXP_TAB[32] = {
 
 // expf as the reference's libm computes it (maple.c:738, 829, 915 call expf): x scaled by 32/ln2, nearest integer
 // split off with the 1.5*2^52 shift, cubic in the remainder, table value times 2^(k/32), one rounding to float.
-__device__ __forceinline__ float dev_expf(float x) {
+template <typename TabT>
+__device__ __forceinline__ float dev_expf_tab(float x, const TabT *tab) {
     if (x != x) return x;
     if (x > 89.0f) return __int_as_float(0x7f800000);
     if (x < -104.0f) return 0.0f;
@@ -27,15 +28,20 @@ __device__ __forceinline__ float dev_expf(float x) {
     unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
     kd -= shift;
     double r = z - kd;
-    double s = __longlong_as_double((long long)(DEV_EXP_TAB[ki & 31] + (ki << 47)));
+    double s = __longlong_as_double((long long)(tab[ki & 31] + (ki << 47)));
     double p = c0 * r + c1, r2 = r * r, y = c2 * r + 1.0;
     y = p * r2 + y;
     return (float)(y * s);
 }
 
+__device__ __forceinline__ float dev_expf(float x) { return dev_expf_tab(x, DEV_EXP_TAB); }
+
 // maple.c:827-829: g = min(g, 7), u = clamp(u, -7, 7), act = g / (1 + expf(-g)) * u
-__device__ __forceinline__ float dev_silu_mul(float g, float u) {
+// tab: the 32-entry table above, or a copy of it in shared memory (lane-varying index: cheaper there)
+template <typename TabT>
+__device__ __forceinline__ float dev_silu_mul_tab(float g, float u, const TabT *tab) {
     g = g < 7.0f ? g : 7.0f;
     u = u < -7.0f ? -7.0f : (u > 7.0f ? 7.0f : u);
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, dev_expf(-g))), u);
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, dev_expf_tab(-g, tab))), u);
 }
+__device__ __forceinline__ float dev_silu_mul(float g, float u) { return dev_silu_mul_tab(g, u, DEV_EXP_TAB); }

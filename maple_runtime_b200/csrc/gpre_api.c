@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
+#include <cuda.h>
 #include <cuda_runtime_api.h>
 #include "../../include/gpre.h"
 #include "../../include/gmoe.h"
@@ -19,6 +20,8 @@
 #define FFN 512
 #define MAXREG 64          /* gpu_pre.m:21 */
 #define MAXSYNTH 64
+#define MAP_CACHE 16384
+#define UMMA_TN 80         /* tokens per tile of the tcgen05 kernels (k_expert_umma.cu) */
 
 static char g_err[512];
 static int fail(const char *who, const char *fmt, ...) {
@@ -33,7 +36,7 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; ExpertPtrs *tab; int set; } LayerDev;
+typedef struct { uint16_t *router, *post_ln; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
 
 static struct {
     int ready, maxtok, maxp, mask_words, keep, path, nb_cur;
@@ -46,6 +49,8 @@ static struct {
     unsigned *mask; int *err, *h_err;
     MoeTile *tiles_a, *tiles_b;
     ExpertPtrs *tab_call;      /* the used experts of one gpre_moe call */
+    ExpertMaps *maps_call, *h_maps; int8_t *hq_sorted; TMap bmap_hq, bmap_aq;
+    struct { const void *key; ExpertMaps m; } *map_cache;   /* tensor maps of experts seen by gpre_moe, by code pointer */
     MoeTile *h_tiles; ExpertPtrs *h_tab;   /* host staging for the reference-shaped calls */
     double t_experts;          /* GPU seconds in gfull_moe, reported by gfull_report */
     float *ring; int ring_nb, ring_n;
@@ -56,6 +61,33 @@ static struct {
 /* ------------------------------------------------------------------------------------------------------------ */
 static int dmalloc(void **p, size_t bytes) { return cudaMalloc(p, bytes ? bytes : 16) == cudaSuccess ? 0 : -1; }
 #define ALLOC(field, bytes) do { if (dmalloc((void **)&S.field, (bytes))) return fail(who, "out of device memory for %d tokens (%s)", maxtok, #field); } while (0)
+
+/* ---- TMA tensor maps (the driver's encoder, reached through the runtime so that libcuda is not a link dependency) ---- */
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode;
+static int tmap_init(const char *who) {
+    if (g_encode) return 0;
+    void *fn = NULL; enum cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn || qr != cudaDriverEntryPointSuccess)
+        return fail(who, "the driver has no cuTensorMapEncodeTiled");
+    g_encode = (EncodeTiledFn)fn; return 0;
+}
+/* rows x width bytes, row pitch bytes; box box_w x box_h; 128-byte swizzle; rows past the end read as zero */
+static int tmap_bytes_2d(const char *who, TMap *out, const void *base, uint64_t width, uint64_t rows, uint64_t pitch, uint32_t box_w, uint32_t box_h) {
+    cuuint64_t gdim[2] = {width, rows}, gstride[1] = {pitch};
+    cuuint32_t box[2] = {box_w, box_h}, estr[2] = {1, 1};
+    CUresult r = g_encode((CUtensorMap *)out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(who, "cuTensorMapEncodeTiled failed (%d) for %p, %llu x %llu", (int)r, base, (unsigned long long)rows, (unsigned long long)width);
+    return 0;
+}
+static int expert_maps(const char *who, const ExpertPtrs *e, ExpertMaps *m) {
+    if (tmap_bytes_2d(who, &m->gate, e->gc, 512, 512, 512, 128, 128) || tmap_bytes_2d(who, &m->up, e->uc, 512, 512, 512, 128, 128) ||
+        tmap_bytes_2d(who, &m->down, e->dc, 128, 2048, 128, 128, 128)) return -1;
+    return 0;
+}
 
 static int init_common(const char *who, int maxtok, int topk) {
     if (topk != TOPK) return fail(who, "topk %d is not supported (the kernels are built for %d)", topk, TOPK);
@@ -79,11 +111,15 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);
     ALLOC(act, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
-    ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16);
+    ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16); ALLOC(maps_call, NEXP * sizeof(ExpertMaps)); ALLOC(hq_sorted, P * HID);
+    if (tmap_init(who)) return -1;
+    if (tmap_bytes_2d(who, &S.bmap_hq, S.hq_sorted, HID, P, HID, 128, UMMA_TN) || tmap_bytes_2d(who, &S.bmap_aq, S.aq, FFN, P, FFN, 128, UMMA_TN)) return -1;
     CU(who, cudaMemset(S.err, 0, 16));
     CU(who, cudaHostAlloc((void **)&S.h_err, 16, cudaHostAllocDefault)); *S.h_err = 0;
     S.h_tiles = malloc(2 * (P / 8 + NEXP) * sizeof(MoeTile)); S.h_tab = malloc(NEXP * sizeof(ExpertPtrs));
-    if (!S.h_tiles || !S.h_tab) return fail(who, "out of host memory");
+    S.h_maps = aligned_alloc(64, NEXP * sizeof(ExpertMaps)); S.map_cache = aligned_alloc(64, MAP_CACHE * sizeof *S.map_cache);
+    if (!S.h_tiles || !S.h_tab || !S.h_maps || !S.map_cache) return fail(who, "out of host memory");
+    memset(S.map_cache, 0, MAP_CACHE * sizeof *S.map_cache);
     S.ready = 1;
     fprintf(stderr, "%s: %s, chunks up to %d tokens, %.0f MB of device workspace, weights resident in HBM\n", who, pr.name, maxtok,
             (double)(T * HID * 13 + P * (FFN * 5 + HID * 4 + 40)) / 1e6);
@@ -154,7 +190,8 @@ static int layer_bufs(const char *who, int L) {
     LayerDev *l = &S.ly[L];
     if (!l->router) {
         if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->post_ln, HID * 2) ||
-            dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs))) return fail(who, "out of device memory for layer %d", L);
+            dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs)) || dmalloc((void **)&l->maps, NEXP * sizeof(ExpertMaps)))
+            return fail(who, "out of device memory for layer %d", L);
     }
     return 0;
 }
@@ -162,7 +199,8 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     if (layer_bufs("gmoe", L)) return -1;
     if (!router || !gloc || !regs) return fail("gmoe", "gmoe_set_layer: null table");
     LayerDev *l = &S.ly[L];
-    for (int e = 0; e < NEXP; e++) if (resolve("gmoe", gloc + e * 12, regs, &S.h_tab[e])) return -1;
+    for (int e = 0; e < NEXP; e++) if (resolve("gmoe", gloc + e * 12, regs, &S.h_tab[e]) || expert_maps("gmoe", &S.h_tab[e], &S.h_maps[e])) return -1;
+    CU("gmoe", cudaMemcpyAsync(l->maps, S.h_maps, NEXP * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     uint16_t ones[HID]; for (int i = 0; i < HID; i++) ones[i] = 0x3F80;
     CU("gmoe", cudaMemcpyAsync(l->router, router, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaMemcpyAsync(l->post_ln, post_ln ? post_ln : ones, HID * 2, cudaMemcpyHostToDevice, S.st));
@@ -183,7 +221,9 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
         const uint8_t *b = w + (size_t)(e - e0) * MS_EXPERT_BYTES; ExpertPtrs *t = &S.h_tab[e];
         t->gc = b; t->gs = (const float *)(b + MS_GU_CODES); t->uc = b + MS_GU_BYTES; t->us = (const float *)(b + MS_GU_BYTES + MS_GU_CODES);
         t->dc = b + 2 * MS_GU_BYTES; t->ds = (const float *)(b + 2 * MS_GU_BYTES + MS_DN_CODES);
+        if (expert_maps("gmoe", t, &S.h_maps[e])) return -1;
     }
+    if (cudaMemcpyAsync(l->maps, S.h_maps, NEXP * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st) != cudaSuccess) return fail("gmoe", "synthetic layer %d: tensor maps", L);
     uint16_t *r = malloc((size_t)NEXP * HID * 2), nw[HID];
     if (!r) return fail("gmoe", "out of host memory");
     msynth_router(seed, L, r); msynth_norm(seed, L, nw);
@@ -234,10 +274,10 @@ int gmoe_profile_read(double *secs, long *launches) {
 static int tile_tn(int nb) { return nb <= 256 ? 8 : 32; }
 
 static int use_umma(int nb) { return S.path == 2 || (S.path == 0 && nb >= 512); }
-static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const int *ue, int nb) {
+static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const ExpertMaps *maps, const int *ue, int nb) {
     memset(a, 0, sizeof *a);
-    a->tab = tab; a->ue = ue; a->ptok = S.utok; a->err = S.err;
-    if (use_umma(nb)) { a->tiles = S.tiles_b; a->ntiles = S.ntiles_b; a->max_tiles = nb * TOPK / 128 + NEXP; }
+    a->tab = tab; a->maps = maps; a->ue = ue; a->ptok = S.utok; a->err = S.err;
+    if (use_umma(nb)) { a->tiles = S.tiles_b; a->ntiles = S.ntiles_b; a->max_tiles = nb * TOPK / UMMA_TN + NEXP; }
     else { a->tiles = S.tiles_a; a->ntiles = S.ntiles_a; a->max_tiles = nb * TOPK / tile_tn(nb) + NEXP; }
     a->hq = S.hq; a->hqs = S.hqs; a->hqsum = S.hqsum; a->act = S.act;
     a->aq = S.aq; a->aqs = S.aqs; a->aqsum = S.aqsum; a->down = S.down;
@@ -245,16 +285,20 @@ static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const int *ue
 }
 static void run_group(int nb) {
     GroupArgs g = {S.top, S.topw, nb, S.mask, S.mask_words, S.nu, S.ue, S.estart, S.ustart, S.utok, S.slot, S.tp, S.uw,
-                   S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tile_tn(nb), 128};
+                   S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tile_tn(nb), UMMA_TN};
     k_group(S.st, &g);
 }
-static void run_experts(const ExpertPtrs *tab, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
-    ExpertArgs a; fill_expert_args(&a, tab, ue, nb);
+static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
+    ExpertArgs a; fill_expert_args(&a, tab, maps, ue, nb);
     int tn = tile_tn(nb);
     int um = use_umma(nb);
-    if (which & 1) { prof_begin(4); if (um) k_gateup_umma(S.st, &a); else k_gateup_mma(S.st, &a, tn); prof_end(4); }
+    if (which & 1) {
+        prof_begin(4);
+        if (um) { k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); k_gateup_umma(S.st, &a, &S.bmap_hq); } else k_gateup_mma(S.st, &a, tn);
+        prof_end(4);
+    }
     if (which & 2) { prof_begin(5); k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK); prof_end(5); }
-    if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a); else k_down_mma(S.st, &a, tn); prof_end(6); }
+    if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6); }
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {
@@ -263,7 +307,7 @@ static void run_layer(int L, int nb, int norm, const float *bias) {
     prof_begin(1); k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3); run_group(nb); prof_end(3);
-    run_experts(l->tab, S.ue, nb, 7);
+    run_experts(l->tab, l->maps, S.ue, nb, 7);
     prof_begin(7);
     if (norm) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb); else k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
     prof_end(7);
@@ -375,16 +419,25 @@ static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc,
     for (int u = 0; u < nu; u++) {
         if (ustart[u + 1] <= ustart[u]) return fail(who, "used expert %d has no pairs", u);
         if (resolve(who, loc + u * 12, regs, &S.h_tab[u])) return -1;
+        {   /* tensor maps of this expert: encoded the first time its codes are seen */
+            size_t hsh = ((uintptr_t)S.h_tab[u].gc >> 8) % MAP_CACHE;
+            if (S.map_cache[hsh].key != (const void *)S.h_tab[u].gc) {
+                if (expert_maps(who, &S.h_tab[u], &S.map_cache[hsh].m)) return -1;
+                S.map_cache[hsh].key = S.h_tab[u].gc;
+            }
+            S.h_maps[u] = S.map_cache[hsh].m;
+        }
         for (int p = ustart[u]; p < ustart[u + 1]; p += tn) {   /* gpu_pre.m:329-333 */
             MoeTile m = {u, p, ustart[u + 1] - p < tn ? ustart[u + 1] - p : tn, 0}; S.h_tiles[nt++] = m;
         }
-        for (int p = ustart[u]; p < ustart[u + 1]; p += 128) {
-            MoeTile m = {u, p, ustart[u + 1] - p < 128 ? ustart[u + 1] - p : 128, 0}; h_tb[ntb++] = m;
+        for (int p = ustart[u]; p < ustart[u + 1]; p += UMMA_TN) {
+            MoeTile m = {u, p, ustart[u + 1] - p < UMMA_TN ? ustart[u + 1] - p : UMMA_TN, 0}; h_tb[ntb++] = m;
         }
     }
     for (int a = 0; a < np; a++) if (ptok[a] < 0 || ptok[a] >= nb) return fail(who, "ptok[%d] = %d", a, ptok[a]);
     for (int i = 0; i < np; i++) if (tp[i] < 0 || tp[i] >= np) return fail(who, "tp[%d] = %d", i, tp[i]);
     CU(who, cudaMemcpyAsync(S.tab_call, S.h_tab, (size_t)nu * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
+    CU(who, cudaMemcpyAsync(S.maps_call, S.h_maps, (size_t)nu * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.ntiles_a, &nt, 4, cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.tiles_b, h_tb, (size_t)ntb * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
@@ -404,7 +457,7 @@ double gpre_moe(const float *x, int nb, int nu, const uint32_t *loc, const int *
     CUD("gpre", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
     cudaEventRecord(S.e0, S.st);
     k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
-    run_experts(S.tab_call, NULL, nb, 7);
+    run_experts(S.tab_call, S.maps_call, NULL, nb, 7);
     k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
     cudaEventRecord(S.e1, S.st);
     CUD("gpre", cudaMemcpyAsync(y, S.y, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
@@ -420,7 +473,7 @@ void gfull_moe(int nu, const uint32_t *loc, const int *regs, const int *ustart, 
     int nb = S.nb_cur;
     if (upload_grouping("gfull", nb, nu, loc, regs, ustart, ptok, pw, tp)) return;
     cudaEventRecord(S.e0, S.st);
-    run_experts(S.tab_call, NULL, nb, 7);            /* hq/hqs/hqsum were left by gmoe_post_norm */
+    run_experts(S.tab_call, S.maps_call, NULL, nb, 7);            /* hq/hqs/hqsum were left by gmoe_post_norm */
     k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
     cudaEventRecord(S.e1, S.st);
     S.fwd_timed = 1;
@@ -479,9 +532,9 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "router_bias")) k_router_logits(S.st, l->router, S.hn, S.bias, S.logits, nb);
     else if (!strcmp(name, "topk")) k_topk(S.st, S.logits, S.top, S.topw, nb);
     else if (!strcmp(name, "group")) run_group(nb);
-    else if (!strcmp(name, "gateup")) run_experts(l->tab, S.ue, nb, 1);
-    else if (!strcmp(name, "actq")) run_experts(l->tab, S.ue, nb, 2);
-    else if (!strcmp(name, "down")) run_experts(l->tab, S.ue, nb, 4);
+    else if (!strcmp(name, "gateup")) run_experts(l->tab, l->maps, S.ue, nb, 1);
+    else if (!strcmp(name, "actq")) run_experts(l->tab, l->maps, S.ue, nb, 2);
+    else if (!strcmp(name, "down")) run_experts(l->tab, l->maps, S.ue, nb, 4);
     else if (!strcmp(name, "combine_y")) k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
     else if (!strcmp(name, "combine_x")) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
     else return fail("gmoe", "no stage named %s", name);

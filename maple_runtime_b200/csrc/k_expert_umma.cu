@@ -1,24 +1,30 @@
 // k_expert_umma.cu -- grouped ternary expert GEMMs on the 5th-generation tensor cores (tcgen05.mma kind::i8), sm_100a.
 //
-// One CTA = one tile (a used expert and up to 128 of its pairs) x one block of 2 x 128 weight rows:
-//   gate+up: 128 gate rows and the 128 up rows of the same index (so the SiLU*up epilogue finds both in one thread);
+// Work item = one tile (a used expert and up to 80 of its pairs) x one block of 2 x 128 weight rows:
+//   gate+up: 128 gate rows and the 128 up rows of the same index (the SiLU*up epilogue finds both in one thread);
 //   down:    two consecutive blocks of 128 down rows.
 // D[128 rows][N tokens] (s32, tensor memory) += A[128 rows][K] (u8 codes 0,1,2) x B[N tokens][K]^T (s8 activations).
+// A persistent grid (one CTA per SM) walks the items; every ring below keeps running across items, so the next item's
+// weights are already on their way while the current one is multiplied.
 //
-// Weights never pass through shared memory: each of 256 threads owns one weight row, reads its 2-bit codes from HBM
-// with 128-bit loads (128 packed bytes = 512 columns per trip, so whole 128-byte lines are consumed), expands every
-// 32-bit word into four code words ((w >> 2s) & 0x03030303 is exactly the four codes of columns 32s+4j..32s+4j+3 of the
-// group, in column order) and writes them with tcgen05.st into the tensor-memory A operand: lane = weight row, one
-// 32-bit cell = four consecutive K values.  The activations (int8, rows gathered by token) are the B operand in shared
-// memory, K-major with the 128-byte swizzle, filled by one warp with 16-byte asynchronous copies.
+// Data movement
+//   weights  HBM -> shared memory, still 2-bit packed: TMA tiled copies (cp.async.bulk.tensor.2d, one tensor map per expert
+//            matrix, box = 128 bytes x 128 rows, 128-byte swizzle), 32 KB stages = 256 rows x 512 columns; the swizzle makes
+//            the later row-per-thread reads free of bank conflicts;
+//   decode   each of 256 threads owns one weight row, reads 32 packed bytes per 128-column block, expands every 32-bit
+//            word with (w >> 2s) & 0x03030303 (the four codes of columns 32s+4j..32s+4j+3 of the group, in column
+//            order; convert.py:29-33) and writes the block with tcgen05.st into the tensor-memory A operand: lane = row,
+//            one 32-bit cell = four consecutive K values.  Decoded weights never touch shared memory;
+//   B        int8 activation rows in pair order (a gather kernel puts the tokens' rows into expert-grouped order first), TMA
+//            tiled copies (box = 128 bytes x 80 rows, 128-byte swizzle = the K-major layout the MMA descriptor names).
 // Arithmetic = maple.c:425-458: out = (float)(sum(code*q) - qsum) * qs * s[r]; integer sums are exact.
 //
-// Roles (320 threads): warps 0-3 A rows of accumulator 0, warps 4-7 A rows of accumulator 1 (all eight do the
-// epilogue), warp 8 B copies, warp 9 issues the MMAs.  Four pipeline stages; per stage a_full (8 warp arrivals),
-// b_full (1), empty (tcgen05.commit).  Every wait is bounded (umma.cuh); on a timeout the CTA raises args.err, frees
-// its tensor memory and returns.
+// Warps (608 threads): 0-3 decode rows of accumulator 0, 4-7 rows of accumulator 1, 8 weight TMA, 9 B TMA, 10 MMA issue,
+// 11-18 epilogue (two accumulator buffers, so an epilogue overlaps the next item's MMAs).
+// Every mbarrier wait is bounded (umma.cuh): on a timeout the CTA raises args.err, frees tensor memory and returns.
 //
-// Tensor memory (512 columns): [0,128) accumulator 0, [128,256) accumulator 1, [256,512) four A stages of 2 x 32 columns.
+// Tensor memory (512 columns): accumulator buffer b at 160 b (acc 0) and 160 b + 80 (acc 1); A stage s at 320 + 64 s
+// (rows of acc 0) and 352 + 64 s (rows of acc 1).
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -28,161 +34,245 @@
 
 extern "C" void k_count_add(long n);
 
-#define UM_STAGES 4
-#define UM_TN 128
-#define UM_BSTAGE (UM_TN * 128)
+#define UM_TN 80
+#define UM_ASTAGES 3
+#define UM_WSTAGES 4
+#define UM_BSTAGES 6
+#define UM_WBYTES (256 * 128)
+#define UM_BBYTES (UM_TN * 128)
+#define UM_ACOL 320
 
 struct __align__(16) UmShared {
-    uint64_t a_full[UM_STAGES], b_full[UM_STAGES], empty[UM_STAGES], acc_full;
+    uint64_t w_full[UM_WSTAGES], w_empty[UM_WSTAGES], a_full[UM_ASTAGES], a_empty[UM_ASTAGES];
+    uint64_t b_full[UM_BSTAGES], b_empty[UM_BSTAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base; int abort_flag;
-    int tok[UM_TN]; float qs[UM_TN]; int qsum[UM_TN];
+    unsigned long long exp_tab[32];
+    float m_qs[8][UM_TN]; int m_qsum[8][UM_TN];      // per epilogue warp: scale and code-sum correction of the tile's tokens
 };
 
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+#ifdef UMMA_TRACE
+__device__ long long g_um_trace[32][4096];
+__device__ int g_um_tn[32];
+#define TR(role, tag) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { int i_ = g_um_tn[role]; if (i_ < 4095) { g_um_trace[role][i_] = (clock64() << 8) | (tag); g_um_tn[role] = i_ + 1; } } } while (0)
+#else
+#define TR(role, tag)
+#endif
 template <int KB, bool GATEUP>
-__global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
+__global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap bmap) {
     extern __shared__ __align__(1024) uint8_t um_smem_raw[];
-    const int tile_i = blockIdx.y;
-    if (tile_i >= *a.ntiles) return;
-    uint8_t *bs = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);          // UM_STAGES x 16 KB, 1024-aligned
-    UmShared *sh = reinterpret_cast<UmShared *>(bs + UM_STAGES * UM_BSTAGE);
-    const MoeTile tile = a.tiles[tile_i];
-    const int ex = a.ue ? a.ue[tile.u] : tile.u;
-    const ExpertPtrs ep = a.tab[ex];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, mb = blockIdx.x;
-    const int cnt = tile.cnt, N = (cnt + 15) & ~15;
-    constexpr int KBYTES = KB * 128;                                                         // bytes of one int8 activation row
+    uint8_t *base = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *wsm = base;                                              // UM_WSTAGES x 32 KB packed weights
+    uint8_t *bsm = base + UM_WSTAGES * UM_WBYTES;                      // UM_BSTAGES x 10 KB int8 activations (1024-aligned: 10240 = 10 x 1024)
+    UmShared *sh = reinterpret_cast<UmShared *>(bsm + UM_BSTAGES * UM_BBYTES);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int MB = GATEUP ? 4 : 8, NSB = KB / 4;
+    const int nitems = *a.ntiles * MB;
     volatile int *abortp = &sh->abort_flag;
 
     if (tid == 0) {
-        for (int s = 0; s < UM_STAGES; s++) { mbar_init(&sh->a_full[s], 8); mbar_init(&sh->b_full[s], 1); mbar_init(&sh->empty[s], 1); }
-        mbar_init(&sh->acc_full, 1); sh->abort_flag = 0; mbar_init_fence();
+        for (int s = 0; s < UM_WSTAGES; s++) { mbar_init(&sh->w_full[s], 1); mbar_init(&sh->w_empty[s], 8); }
+        for (int s = 0; s < UM_ASTAGES; s++) { mbar_init(&sh->a_full[s], 8); mbar_init(&sh->a_empty[s], 1); }
+        for (int s = 0; s < UM_BSTAGES; s++) { mbar_init(&sh->b_full[s], 1); mbar_init(&sh->b_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&sh->acc_full[s], 1); mbar_init(&sh->acc_empty[s], 8); }
+        sh->abort_flag = 0; mbar_init_fence();
     }
-    if (warp == 9) tmem_alloc(&sh->tmem_base, 512);
-    if (tid < cnt) {
-        int pair = tile.p0 + tid;
-        if (GATEUP) { int t = a.ptok[pair]; sh->tok[tid] = t; sh->qs[tid] = a.hqs[t]; sh->qsum[tid] = a.hqsum[t]; }
-        else { sh->tok[tid] = pair; sh->qs[tid] = a.aqs[pair]; sh->qsum[tid] = a.aqsum[pair]; }
-    }
+    if (tid < 32) sh->exp_tab[tid] = DEV_EXP_TAB[tid];
+    if (warp == 10) tmem_alloc(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tb = sh->tmem_base;
+    bool live = true;
 
     if (warp < 8) {
-        // ---------------- A producer: one weight row per thread ----------------
-        const int h = warp >> 2, row = (warp & 3) * 32 + lane;
-        const uint8_t *wrow = GATEUP ? (h ? ep.uc : ep.gc) + (size_t)(mb * 128 + row) * (KBYTES / 4)
-                                     : ep.dc + (size_t)((mb * 2 + h) * 128 + row) * (KBYTES / 4);
-        const uint32_t a_lane = tb + ((uint32_t)((warp & 3) * 32) << 16) + 256 + h * 32;
-        constexpr int NSB = KB / 4;                                                          // trips of 128 packed bytes
-        uint4 cur[8], nxt[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) nxt[i] = __ldg(reinterpret_cast<const uint4 *>(wrow) + i);
-        bool live = true;
+        // ---------------- decode: one weight row per thread, packed bytes from the shared-memory ring ----------------
+        const int h = warp >> 2, R = h * 128 + (warp & 3) * 32 + lane;
+        const uint32_t a_lane = tb + ((uint32_t)((warp & 3) * 32) << 16) + UM_ACOL + h * 32;
+        uint32_t wcnt = 0, acnt = 0;
+        for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
 #pragma unroll 1
-        for (int sb = 0; sb < NSB && live; sb++) {
+            for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
+                const int ws = wcnt % UM_WSTAGES;
+                TR(warp, 1);
+                if (!mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp)) { live = false; break; }
+                TR(warp, 2);
+                const uint8_t *wr = wsm + ws * UM_WBYTES + R * 128;
 #pragma unroll
-            for (int i = 0; i < 8; i++) cur[i] = nxt[i];
-            if (sb + 1 < NSB) {
+                for (int q = 0; q < 4; q++, acnt++) {
+                    const uint4 v0 = *reinterpret_cast<const uint4 *>(wr + (((2 * q) ^ (R & 7)) << 4));
+                    const uint4 v1 = *reinterpret_cast<const uint4 *>(wr + (((2 * q + 1) ^ (R & 7)) << 4));
+                    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    uint32_t r[32];
 #pragma unroll
-                for (int i = 0; i < 8; i++) nxt[i] = __ldg(reinterpret_cast<const uint4 *>(wrow + (sb + 1) * 128) + i);
-            }
+                    for (int sft = 0; sft < 4; sft++)
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int kb = sb * 4 + q, s = kb % UM_STAGES, it = kb / UM_STAGES;
-                if (!mbar_wait(&sh->empty[s], (it & 1) ^ 1, abortp)) { live = false; break; }
-                tc_fence_after();
-                if (a.dbg & 2) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->a_full[s]); continue; }
-                const uint32_t w[8] = {cur[2 * q].x, cur[2 * q].y, cur[2 * q].z, cur[2 * q].w, cur[2 * q + 1].x, cur[2 * q + 1].y, cur[2 * q + 1].z, cur[2 * q + 1].w};
-                uint32_t r[32];
-#pragma unroll
-                for (int sft = 0; sft < 4; sft++)
-#pragma unroll
-                    for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
-                tmem_st32(a_lane + s * 64, r);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->a_full[s]);
-            }
-        }
-        // ---------------- epilogue: lane = weight row, columns = tokens ----------------
-        if (live && mbar_wait(&sh->acc_full, 0, abortp) && !(a.dbg & 8)) {
-            tc_fence_after();
-            const uint32_t d_lane = tb + ((uint32_t)((warp & 3) * 32) << 16);
-            const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
-            const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
-            for (int c0 = h * 16; c0 < N; c0 += 32) {                                        // 16-column pieces, alternating between the two warp sets
-                uint32_t v0[16], v1[16];
-                tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 128 + c0, v1);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int n = c0 + j;
-                    if (n < cnt) {
-                        const int pair = tile.p0 + n, d0 = (int)v0[j] - sh->qsum[n], d1 = (int)v1[j] - sh->qsum[n];
-                        const float qs = sh->qs[n];
-                        const float f0 = __fmul_rn(__fmul_rn((float)d0, qs), s0), f1 = __fmul_rn(__fmul_rn((float)d1, qs), s1);
-                        if (GATEUP) {
-                            a.act[(size_t)pair * 512 + r0] = dev_silu_mul(f0, f1);
-                            if (a.gate) { a.gate[(size_t)pair * 512 + r0] = f0; a.up[(size_t)pair * 512 + r0] = f1; }
-                            if (a.gu_dots) { a.gu_dots[(size_t)pair * 1024 + r0] = d0; a.gu_dots[(size_t)pair * 1024 + 512 + r0] = d1; }
-                        } else {
-                            a.down[(size_t)pair * 2048 + r0] = f0; a.down[(size_t)pair * 2048 + r0 + 128] = f1;
-                            if (a.dn_dots) { a.dn_dots[(size_t)pair * 2048 + r0] = d0; a.dn_dots[(size_t)pair * 2048 + r0 + 128] = d1; }
-                        }
-                    }
+                        for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
+                    const int as = acnt % UM_ASTAGES;
+                    TR(warp, 3);
+                    if (!mbar_wait(&sh->a_empty[as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp)) { live = false; break; }
+                    TR(warp, 4);
+                    tc_fence_after();
+                    tmem_st32(a_lane + as * 64, r);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->a_full[as]);
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->w_empty[ws]);
             }
         }
     } else if (warp == 8) {
-        // ---------------- B producer: gathered int8 rows, 16-byte asynchronous copies, two stages ahead ----------------
-        const int8_t *src = GATEUP ? a.hq : a.aq;
-        constexpr int AHEAD = 2;
-        bool live = true;
-        for (int kb = 0; kb < KB + AHEAD; kb++) {
-            if (kb < KB && live) {
-                const int s = kb % UM_STAGES, it = kb / UM_STAGES;
-                if (!mbar_wait(&sh->empty[s], (it & 1) ^ 1, abortp)) live = false;
-                else {
-                    const uint32_t dst = smem_u32(bs + s * UM_BSTAGE);
-                    for (int i = lane; i < cnt * 8 && !(a.dbg & 1); i += 32) {
-                        const int n = i >> 3, c = i & 7;
-                        cp_async16(dst + n * 128 + ((c ^ (n & 7)) << 4), src + (size_t)sh->tok[n] * KBYTES + kb * 128 + c * 16);
+        // ---------------- weight TMA (one lane): per stage the 128 rows of accumulator 0 and the 128 of accumulator 1 ----------------
+        if (lane == 0) {
+            uint32_t wcnt = 0;
+            for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
+                const MoeTile tile = a.tiles[item / MB];
+                const int mb = item % MB, ex = a.ue ? a.ue[tile.u] : tile.u;
+                const ExpertMaps *em = a.maps + ex;
+                for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
+                    const int ws = wcnt % UM_WSTAGES;
+                    TR(warp, 1);
+                    if (!mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
+                    TR(warp, 2);
+                    const uint32_t dst = smem_u32(wsm + ws * UM_WBYTES);
+                    mbar_expect_tx(&sh->w_full[ws], UM_WBYTES);
+                    if (GATEUP) {
+                        tma_load_2d(dst, &em->gate, sb * 128, mb * 128, &sh->w_full[ws]);
+                        tma_load_2d(dst + 128 * 128, &em->up, sb * 128, mb * 128, &sh->w_full[ws]);
+                    } else {
+                        tma_load_2d(dst, &em->down, 0, mb * 256, &sh->w_full[ws]);
+                        tma_load_2d(dst + 128 * 128, &em->down, 0, mb * 256 + 128, &sh->w_full[ws]);
+                    }
+                    TR(warp, 3);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- B TMA (one lane): 80 rows x 128 bytes of the pair-ordered int8 activations per stage ----------------
+        if (lane == 0) {
+            uint32_t bcnt = 0;
+            for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
+                const MoeTile tile = a.tiles[item / MB];
+                for (int kb = 0; kb < KB && live; kb++, bcnt++) {
+                    const int s = bcnt % UM_BSTAGES;
+                    TR(warp, 1);
+                    if (!mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
+                    TR(warp, 2);
+                    mbar_expect_tx(&sh->b_full[s], UM_BBYTES);
+                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES), &bmap, kb * 128, tile.p0, &sh->b_full[s]);
+                    TR(warp, 3);
+                }
+            }
+        }
+    } else if (warp == 10) {
+        // ---------------- MMA issue (one lane) ----------------
+        if (lane == 0) {
+            uint32_t acnt = 0, bcnt = 0, icnt = 0;
+            for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
+                const MoeTile tile = a.tiles[item / MB];
+                const uint32_t idesc = idesc_i8_u8s8((uint32_t)((tile.cnt + 15) & ~15));
+                const int buf = icnt & 1;
+                TR(warp, 1);
+                if (!mbar_wait(&sh->acc_empty[buf], ((icnt >> 1) & 1) ^ 1, abortp)) { live = false; break; }
+                TR(warp, 2);
+                tc_fence_after();
+                const uint32_t d0 = tb + buf * 160, d1 = d0 + 80;
+                for (int kb = 0; kb < KB && live; kb++, acnt++, bcnt++) {
+                    const int as = acnt % UM_ASTAGES, bs = bcnt % UM_BSTAGES;
+                    if (!mbar_wait(&sh->a_full[as], (acnt / UM_ASTAGES) & 1, abortp)) { live = false; break; }
+                    TR(warp, 3);
+                    if (!mbar_wait(&sh->b_full[bs], (bcnt / UM_BSTAGES) & 1, abortp)) { live = false; break; }
+                    TR(warp, 4);
+                    tc_fence_after();
+                    const uint32_t bbase = smem_u32(bsm + bs * UM_BBYTES), acol = tb + UM_ACOL + as * 64;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint64_t bd = smem_desc_k128(bbase, k * 32);
+                        umma_i8_ts(d0, acol + k * 8, bd, idesc, (kb | k) != 0);
+                        umma_i8_ts(d1, acol + 32 + k * 8, bd, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&sh->a_empty[as]);
+                    umma_commit(&sh->b_empty[bs]);
+                }
+                if (live) umma_commit(&sh->acc_full[buf]);
+                TR(warp, 5);
+            }
+        }
+    } else {
+        // ---------------- epilogue: lane = weight row, columns = tokens; warps 11-14 take the even 16-column pieces, 15-18 the odd ----------------
+        const int ew = warp - 11, q4 = warp & 3, half = ew >> 2, row = q4 * 32 + lane;   // a warp reaches the tensor-memory lanes 32 (warp % 4) ..
+        uint32_t icnt = 0;
+        for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
+            const MoeTile tile = a.tiles[item / MB];
+            const int mb = item % MB, ex = a.ue ? a.ue[tile.u] : tile.u, cnt = tile.cnt, N = (cnt + 15) & ~15;
+            const ExpertPtrs ep = a.tab[ex];
+            const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
+            const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
+            const int buf = icnt & 1;
+            __syncwarp();
+            for (int n = lane; n < N; n += 32) {
+                const int pair = tile.p0 + (n < cnt ? n : 0), t = GATEUP ? a.ptok[pair] : pair;
+                sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
+            }
+            __syncwarp();
+            TR(warp, 1);
+            if (!mbar_wait(&sh->acc_full[buf], (icnt >> 1) & 1, abortp)) { live = false; break; }
+            TR(warp, 2);
+            tc_fence_after();
+            const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16) + buf * 160;
+            const int c_last = ((N / 16 - 1 - half) & ~1) + half;           // this warp's last piece (negative: none)
+            if (half * 16 >= N) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->acc_empty[buf]); }
+            for (int c0 = half * 16; c0 < N; c0 += 32) {
+                uint32_t v0[16], v1[16];
+                tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 80 + c0, v1);
+                tmem_ld_wait();
+                if (c0 == c_last * 16) {   // the buffer is in registers: hand it back before the arithmetic
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+                    TR(warp, 3);
+                }
+                float o0[16], o1[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int qsum = sh->m_qsum[ew][c0 + j]; const float qs = sh->m_qs[ew][c0 + j];
+                    const int d0 = (int)v0[j] - qsum, d1 = (int)v1[j] - qsum;
+                    o0[j] = __fmul_rn(__fmul_rn((float)d0, qs), s0); o1[j] = __fmul_rn(__fmul_rn((float)d1, qs), s1);
+                    v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
+                }
+                if (GATEUP) {
+                    if (a.gate) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
+                            const size_t pair = (size_t)(tile.p0 + c0 + j);
+                            a.gate[pair * 512 + r0] = o0[j]; a.up[pair * 512 + r0] = o1[j];
+                            a.gu_dots[pair * 1024 + r0] = (int)v0[j]; a.gu_dots[pair * 1024 + 512 + r0] = (int)v1[j];
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) o0[j] = dev_silu_mul_tab(o0[j], o1[j], sh->exp_tab);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) a.act[(size_t)(tile.p0 + c0 + j) * 512 + r0] = o0[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
+                        const size_t pair = (size_t)(tile.p0 + c0 + j);
+                        a.down[pair * 2048 + r0] = o0[j]; a.down[pair * 2048 + r0 + 128] = o1[j];
+                        if (a.dn_dots) { a.dn_dots[pair * 2048 + r0] = (int)v0[j]; a.dn_dots[pair * 2048 + r0 + 128] = (int)v1[j]; }
                     }
                 }
             }
-            cp_async_commit();
-            if (kb >= AHEAD) {
-                cp_async_wait<AHEAD>();
-                proxy_fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->b_full[(kb - AHEAD) % UM_STAGES]);
-            }
         }
-        cp_async_wait<0>();
-    } else if (lane == 0) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = idesc_i8_u8s8((uint32_t)N);
-        bool live = true;
-        for (int kb = 0; kb < KB && live; kb++) {
-            const int s = kb % UM_STAGES, it = kb / UM_STAGES;
-            if (!mbar_wait(&sh->a_full[s], it & 1, abortp) || !mbar_wait(&sh->b_full[s], it & 1, abortp)) { live = false; break; }
-            tc_fence_after();
-            const uint32_t bbase = smem_u32(bs + s * UM_BSTAGE);
-#pragma unroll
-            for (int k = 0; k < 4 && !(a.dbg & 4); k++) {
-                const uint64_t bd = smem_desc_k128(bbase, k * 32);
-                umma_i8_ts(tb, tb + 256 + s * 64 + k * 8, bd, idesc, (kb | k) != 0);
-                umma_i8_ts(tb + 128, tb + 256 + s * 64 + 32 + k * 8, bd, idesc, (kb | k) != 0);
-            }
-            umma_commit(&sh->empty[s]);
-        }
-        if (live) umma_commit(&sh->acc_full);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 10) {
+        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tb, 512);
         if (lane == 0 && sh->abort_flag && a.err) *a.err = 1;
@@ -190,16 +280,31 @@ __global__ void __launch_bounds__(320, 1) expert_umma_kernel(ExpertArgs a) {
 }
 
 template <int KB, bool GATEUP>
-static void launch(cudaStream_t st, const ExpertArgs *a) {
-    const size_t smem = (size_t)UM_STAGES * UM_BSTAGE + sizeof(UmShared) + 1024;
-    static bool attr_done = false;
-    if (!attr_done) { cudaFuncSetAttribute(expert_umma_kernel<KB, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
-    dim3 grid(GATEUP ? 4 : 8, a->max_tiles);
-    ExpertArgs b = *a;
-    static int dbg = -1; if (dbg < 0) { const char *e = getenv("GMOE_UMMA_DBG"); dbg = e ? atoi(e) : 0; }
-    b.dbg = dbg;
-    expert_umma_kernel<KB, GATEUP><<<grid, 320, smem, st>>>(b);
+static void launch(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) {
+    const size_t smem = (size_t)UM_WSTAGES * UM_WBYTES + UM_BSTAGES * UM_BBYTES + sizeof(UmShared) + 1024;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(expert_umma_kernel<KB, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    expert_umma_kernel<KB, GATEUP><<<sms, 608, smem, st>>>(*a, *bmap);
     k_count_add(1);
 }
-extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a) { if (a->max_tiles > 0) launch<16, true>(st, a); }
-extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a) { if (a->max_tiles > 0) launch<4, false>(st, a); }
+extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) { if (a->max_tiles > 0) launch<16, true>(st, a, bmap); }
+extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) { if (a->max_tiles > 0) launch<4, false>(st, a, bmap); }
+
+// ---- rows of the per-token int8 matrix copied into pair (expert-grouped) order: the B operand the TMA can tile ----
+__global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restrict__ src, const int *__restrict__ rows, int8_t *__restrict__ dst, int np) {
+    const int pair = blockIdx.x * 2 + (threadIdx.x >> 7), c = threadIdx.x & 127;
+    if (pair >= np) return;
+    reinterpret_cast<uint4 *>(dst + (size_t)pair * 2048)[c] = reinterpret_cast<const uint4 *>(src + (size_t)rows[pair] * 2048)[c];
+}
+extern "C" void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np) {
+    if (np <= 0) return;
+    gather_rows_kernel<<<(np + 1) / 2, 256, 0, st>>>(src, rows, dst, np);
+    k_count_add(1);
+}
+#ifdef UMMA_TRACE
+extern "C" void k_umma_trace_reset(void) { int z[32] = {0}; cudaMemcpyToSymbol(g_um_tn, z, sizeof z); }
+extern "C" void k_umma_trace_dump(long long *host, int *n) { cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_um_trace, sizeof(long long) * 32 * 4096); cudaMemcpyFromSymbol(n, g_um_tn, sizeof(int) * 32); }
+#endif

@@ -10,11 +10,15 @@ extern "C" {
 
 /* where one expert's six arrays live in HBM (built from the reference's GLOC/GREG tables, maple.c:1106-1131) */
 typedef struct { const uint8_t *gc, *uc, *dc; const float *gs, *us, *ds; } ExpertPtrs;
+/* an opaque 128-byte TMA tensor map (CUtensorMap), and the three weight matrices of one expert as 2-D byte tensors */
+typedef struct __attribute__((aligned(64))) { unsigned char b[128]; } TMap;
+typedef struct { TMap gate, up, down; } ExpertMaps;
 /* one unit of grouped-GEMM work: used expert u, first pair p0, cnt pairs (gpu_pre.m:329-333 uses the same triple) */
 typedef struct { int u, p0, cnt, pad; } MoeTile;
 
 typedef struct {
     const ExpertPtrs *tab;   /* indexed by ue[u] when ue != NULL, else by u */
+    const ExpertMaps *maps;  /* same indexing; only the tcgen05 kernels read it */
     const int *ue;
     const MoeTile *tiles; const int *ntiles; int max_tiles;
     const int *ptok;         /* [np] token of each pair */
@@ -27,7 +31,6 @@ typedef struct {
     /* optional stage outputs (NULL = off) */
     float *gate, *up; int32_t *gu_dots, *dn_dots;
     int *err;                /* set to 1 by a kernel whose bounded wait ran out */
-    int dbg;                 /* timing experiments only (GMOE_UMMA_DBG): bit 0 no B copies, 1 no A decode/store, 2 no MMA, 3 no epilogue */
 } ExpertArgs;
 
 void k_count_reset(void); long k_count(void);
@@ -50,9 +53,12 @@ void k_combine(cudaStream_t st, const float *down, const float *uw, const int *t
 void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 
-/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */
-void k_gateup_umma(cudaStream_t st, const ExpertArgs *a);
-void k_down_umma(cudaStream_t st, const ExpertArgs *a);
+/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 80 tokens, codes decoded in registers into tensor memory */
+/* bmap: tensor map over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down), box 128 x 80 */
+void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
+void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
+/* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
+void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
 
 void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
 
