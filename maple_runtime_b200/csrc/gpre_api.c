@@ -110,7 +110,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(ustart, (NEXP + 1) * 4); ALLOC(utok, P * 4); ALLOC(uw, P * 4); ALLOC(slot, P * 4); ALLOC(tp, P * 4);
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);
-    ALLOC(act, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
+    ALLOC(act, P * FFN * 4); ALLOC(gate, P * FFN * 4); ALLOC(up, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
     ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16); ALLOC(maps_call, NEXP * sizeof(ExpertMaps)); ALLOC(hq_sorted, P * HID);
     if (tmap_init(who)) return -1;
     if (tmap_bytes_2d(who, &S.bmap_hq, S.hq_sorted, HID, P, HID, 128, UMMA_TN) || tmap_bytes_2d(who, &S.bmap_aq, S.aq, FFN, P, FFN, 128, UMMA_TN)) return -1;
@@ -131,7 +131,7 @@ int gmoe_set_device(int dev) { CU("gmoe", cudaSetDevice(dev)); return 0; }
 
 static int keep_alloc(const char *who) {
     int maxtok = S.maxtok; size_t P = (size_t)S.maxp;
-    if (!S.gate) { ALLOC(gate, P * FFN * 4); ALLOC(up, P * FFN * 4); ALLOC(gu_dots, P * 2 * FFN * 4); ALLOC(dn_dots, P * HID * 4); }
+    if (!S.gu_dots) { ALLOC(gu_dots, P * 2 * FFN * 4); ALLOC(dn_dots, P * HID * 4); }
     return 0;
 }
 int gmoe_keep_stages(int keep) {
@@ -281,7 +281,8 @@ static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const ExpertM
     else { a->tiles = S.tiles_a; a->ntiles = S.ntiles_a; a->max_tiles = nb * TOPK / tile_tn(nb) + NEXP; }
     a->hq = S.hq; a->hqs = S.hqs; a->hqsum = S.hqsum; a->act = S.act;
     a->aq = S.aq; a->aqs = S.aqs; a->aqsum = S.aqsum; a->down = S.down;
-    if (S.keep) { a->gate = S.gate; a->up = S.up; a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
+    if (S.keep || use_umma(nb)) { a->gate = S.gate; a->up = S.up; }          /* the tensor-core GEMM always stores gate and up */
+    if (S.keep) { a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
 }
 static void run_group(int nb) {
     GroupArgs g = {S.top, S.topw, nb, S.mask, S.mask_words, S.nu, S.ue, S.estart, S.ustart, S.utok, S.slot, S.tp, S.uw,
@@ -297,7 +298,12 @@ static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int
         if (um) { k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); k_gateup_umma(S.st, &a, &S.bmap_hq); } else k_gateup_mma(S.st, &a, tn);
         prof_end(4);
     }
-    if (which & 2) { prof_begin(5); k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK); prof_end(5); }
+    if (which & 2) {
+        prof_begin(5);
+        if (um) k_silu_quant(S.st, S.gate, S.up, S.keep ? S.act : NULL, S.aq, S.aqs, S.aqsum, nb * TOPK);
+        else k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK);
+        prof_end(5);
+    }
     if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6); }
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */

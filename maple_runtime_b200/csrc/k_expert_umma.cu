@@ -55,11 +55,11 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
 }
 
 #ifdef UMMA_TRACE
-__device__ long long g_um_trace[32][4096];
-__device__ int g_um_tn[32];
-#define TR(role, tag) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { int i_ = g_um_tn[role]; if (i_ < 4095) { g_um_trace[role][i_] = (clock64() << 8) | (tag); g_um_tn[role] = i_ + 1; } } } while (0)
+// timing build: every bounded wait adds its duration to a per-warp register counter; CTA 0 stores them at the end
+__device__ long long g_um_trace[32][8];
+#define TWAIT(id, call) ([&]() { long long t_ = clock64(); bool ok_ = (call); wacc[id] += clock64() - t_; return ok_; }())
 #else
-#define TR(role, tag)
+#define TWAIT(id, call) (call)
 #endif
 template <int KB, bool GATEUP>
 __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap bmap) {
@@ -87,6 +87,9 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
     tc_fence_after();
     const uint32_t tb = sh->tmem_base;
     bool live = true;
+#ifdef UMMA_TRACE
+    long long wacc[4] = {0, 0, 0, 0}; const long long t_begin = clock64();
+#endif
 
     if (warp < 8) {
         // ---------------- decode: one weight row per thread, packed bytes from the shared-memory ring ----------------
@@ -97,9 +100,7 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll 1
             for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
                 const int ws = wcnt % UM_WSTAGES;
-                TR(warp, 1);
-                if (!mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp)) { live = false; break; }
-                TR(warp, 2);
+                if (!TWAIT(0, mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp))) { live = false; break; }
                 const uint8_t *wr = wsm + ws * UM_WBYTES + R * 128;
 #pragma unroll
                 for (int q = 0; q < 4; q++, acnt++) {
@@ -112,9 +113,7 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll
                         for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
                     const int as = acnt % UM_ASTAGES;
-                    TR(warp, 3);
-                    if (!mbar_wait(&sh->a_empty[as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp)) { live = false; break; }
-                    TR(warp, 4);
+                    if (!TWAIT(1, mbar_wait(&sh->a_empty[as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     tc_fence_after();
                     tmem_st32(a_lane + as * 64, r);
                     tmem_st_wait();
@@ -136,9 +135,7 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                 const ExpertMaps *em = a.maps + ex;
                 for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
                     const int ws = wcnt % UM_WSTAGES;
-                    TR(warp, 1);
-                    if (!mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
-                    TR(warp, 2);
+                    if (!TWAIT(0, mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     const uint32_t dst = smem_u32(wsm + ws * UM_WBYTES);
                     mbar_expect_tx(&sh->w_full[ws], UM_WBYTES);
                     if (GATEUP) {
@@ -148,7 +145,6 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                         tma_load_2d(dst, &em->down, 0, mb * 256, &sh->w_full[ws]);
                         tma_load_2d(dst + 128 * 128, &em->down, 0, mb * 256 + 128, &sh->w_full[ws]);
                     }
-                    TR(warp, 3);
                 }
             }
         }
@@ -160,47 +156,44 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                 const MoeTile tile = a.tiles[item / MB];
                 for (int kb = 0; kb < KB && live; kb++, bcnt++) {
                     const int s = bcnt % UM_BSTAGES;
-                    TR(warp, 1);
-                    if (!mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
-                    TR(warp, 2);
+                    if (!TWAIT(0, mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     mbar_expect_tx(&sh->b_full[s], UM_BBYTES);
                     tma_load_2d(smem_u32(bsm + s * UM_BBYTES), &bmap, kb * 128, tile.p0, &sh->b_full[s]);
-                    TR(warp, 3);
                 }
             }
         }
     } else if (warp == 10) {
-        // ---------------- MMA issue (one lane) ----------------
+        // ---------------- MMA issue (one lane).  Stage indices and parities are carried in registers (wrap by compare, no
+        // division), descriptors and column addresses are base + stage * constant: the thread's instructions go to the MMAs ----------------
         if (lane == 0) {
-            uint32_t acnt = 0, bcnt = 0, icnt = 0;
+            const uint64_t bdesc0 = smem_desc_k128(smem_u32(bsm), 0);
+            const uint32_t afull0 = smem_u32(&sh->a_full[0]), aempty0 = smem_u32(&sh->a_empty[0]);
+            const uint32_t bfull0 = smem_u32(&sh->b_full[0]), bempty0 = smem_u32(&sh->b_empty[0]);
+            uint32_t as = 0, ap = 0, bs = 0, bp = 0, icnt = 0;
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
                 const MoeTile tile = a.tiles[item / MB];
                 const uint32_t idesc = idesc_i8_u8s8((uint32_t)((tile.cnt + 15) & ~15));
                 const int buf = icnt & 1;
-                TR(warp, 1);
-                if (!mbar_wait(&sh->acc_empty[buf], ((icnt >> 1) & 1) ^ 1, abortp)) { live = false; break; }
-                TR(warp, 2);
+                if (!TWAIT(0, mbar_wait(&sh->acc_empty[buf], ((icnt >> 1) & 1) ^ 1, abortp))) { live = false; break; }
                 tc_fence_after();
                 const uint32_t d0 = tb + buf * 160, d1 = d0 + 80;
-                for (int kb = 0; kb < KB && live; kb++, acnt++, bcnt++) {
-                    const int as = acnt % UM_ASTAGES, bs = bcnt % UM_BSTAGES;
-                    if (!mbar_wait(&sh->a_full[as], (acnt / UM_ASTAGES) & 1, abortp)) { live = false; break; }
-                    TR(warp, 3);
-                    if (!mbar_wait(&sh->b_full[bs], (bcnt / UM_BSTAGES) & 1, abortp)) { live = false; break; }
-                    TR(warp, 4);
+#pragma unroll 1
+                for (int kb = 0; kb < KB; kb++) {
+                    if (!TWAIT(1, mbar_wait_addr(afull0 + as * 8, ap, abortp)) || !TWAIT(2, mbar_wait_addr(bfull0 + bs * 8, bp, abortp))) { live = false; break; }
                     tc_fence_after();
-                    const uint32_t bbase = smem_u32(bsm + bs * UM_BBYTES), acol = tb + UM_ACOL + as * 64;
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const uint64_t bd = smem_desc_k128(bbase, k * 32);
-                        umma_i8_ts(d0, acol + k * 8, bd, idesc, (kb | k) != 0);
-                        umma_i8_ts(d1, acol + 32 + k * 8, bd, idesc, (kb | k) != 0);
-                    }
-                    umma_commit(&sh->a_empty[as]);
-                    umma_commit(&sh->b_empty[bs]);
+                    const uint32_t acol = tb + UM_ACOL + as * 64;
+                    const uint64_t bd = bdesc0 + (uint64_t)(bs * (UM_BBYTES >> 4));
+                    const uint32_t acc = kb != 0;
+                    umma_i8_ts(d0, acol, bd, idesc, acc);          umma_i8_ts(d1, acol + 32, bd, idesc, acc);
+                    umma_i8_ts(d0, acol + 8, bd + 2, idesc, 1);    umma_i8_ts(d1, acol + 40, bd + 2, idesc, 1);
+                    umma_i8_ts(d0, acol + 16, bd + 4, idesc, 1);   umma_i8_ts(d1, acol + 48, bd + 4, idesc, 1);
+                    umma_i8_ts(d0, acol + 24, bd + 6, idesc, 1);   umma_i8_ts(d1, acol + 56, bd + 6, idesc, 1);
+                    umma_commit_addr(aempty0 + as * 8);
+                    umma_commit_addr(bempty0 + bs * 8);
+                    if (++as == UM_ASTAGES) { as = 0; ap ^= 1; }
+                    if (++bs == UM_BSTAGES) { bs = 0; bp ^= 1; }
                 }
                 if (live) umma_commit(&sh->acc_full[buf]);
-                TR(warp, 5);
             }
         }
     } else {
@@ -220,9 +213,7 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                 sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
             }
             __syncwarp();
-            TR(warp, 1);
-            if (!mbar_wait(&sh->acc_full[buf], (icnt >> 1) & 1, abortp)) { live = false; break; }
-            TR(warp, 2);
+            if (!TWAIT(0, mbar_wait(&sh->acc_full[buf], (icnt >> 1) & 1, abortp))) { live = false; break; }
             tc_fence_after();
             const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16) + buf * 160;
             const int c_last = ((N / 16 - 1 - half) & ~1) + half;           // this warp's last piece (negative: none)
@@ -235,7 +226,6 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
-                    TR(warp, 3);
                 }
                 float o0[16], o1[16];
 #pragma unroll
@@ -246,18 +236,12 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                     v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
                 }
                 if (GATEUP) {
-                    if (a.gate) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
-                            const size_t pair = (size_t)(tile.p0 + c0 + j);
-                            a.gate[pair * 512 + r0] = o0[j]; a.up[pair * 512 + r0] = o1[j];
-                            a.gu_dots[pair * 1024 + r0] = (int)v0[j]; a.gu_dots[pair * 1024 + 512 + r0] = (int)v1[j];
-                        }
+                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
+                        const size_t pair = (size_t)(tile.p0 + c0 + j);
+                        a.gate[pair * 512 + r0] = o0[j]; a.up[pair * 512 + r0] = o1[j];
+                        if (a.gu_dots) { a.gu_dots[pair * 1024 + r0] = (int)v0[j]; a.gu_dots[pair * 1024 + 512 + r0] = (int)v1[j]; }
                     }
-#pragma unroll
-                    for (int j = 0; j < 16; j++) o0[j] = dev_silu_mul_tab(o0[j], o1[j], sh->exp_tab);
-#pragma unroll
-                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) a.act[(size_t)(tile.p0 + c0 + j) * 512 + r0] = o0[j];
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
@@ -269,6 +253,9 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
             }
         }
     }
+#ifdef UMMA_TRACE
+    if (blockIdx.x == 0 && lane == 0) { for (int i = 0; i < 4; i++) g_um_trace[warp][i] = wacc[i]; g_um_trace[warp][4] = clock64() - t_begin; }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 10) {
@@ -305,6 +292,6 @@ extern "C" void k_gather_rows(cudaStream_t st, const int8_t *src, const int *row
     k_count_add(1);
 }
 #ifdef UMMA_TRACE
-extern "C" void k_umma_trace_reset(void) { int z[32] = {0}; cudaMemcpyToSymbol(g_um_tn, z, sizeof z); }
-extern "C" void k_umma_trace_dump(long long *host, int *n) { cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_um_trace, sizeof(long long) * 32 * 4096); cudaMemcpyFromSymbol(n, g_um_tn, sizeof(int) * 32); }
+extern "C" void k_umma_trace_reset(void) {}
+extern "C" void k_umma_trace_dump(long long *host, int *n) { (void)n; cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_um_trace, sizeof(long long) * 32 * 8); }
 #endif

@@ -360,6 +360,50 @@ extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs
 }
 
 // ------------------------------------------------------------------------------------------------------------
+// SiLU*up + int8 in one pass (maple.c:825-832) for the tensor-core path, whose GEMM stores gate and up: one warp per
+// pair, 16 values per lane.  act (optional) receives the fp32 activations for stage comparisons.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
+                                                         int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np) {
+    __shared__ unsigned long long tab[32];
+    if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, a = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (a >= np) return;
+    const float4 *gr = reinterpret_cast<const float4 *>(gate + (size_t)a * FFN) + lane * 4;
+    const float4 *ur = reinterpret_cast<const float4 *>(up + (size_t)a * FFN) + lane * 4;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float4 g = gr[i], u = ur[i];
+        v[4 * i] = dev_silu_mul_tab(g.x, u.x, tab); v[4 * i + 1] = dev_silu_mul_tab(g.y, u.y, tab);
+        v[4 * i + 2] = dev_silu_mul_tab(g.z, u.z, tab); v[4 * i + 3] = dev_silu_mul_tab(g.w, u.w, tab);
+    }
+    if (act) {
+        float4 *o = reinterpret_cast<float4 *>(act + (size_t)a * FFN) + lane * 4;
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
+    int tot = 0; uint32_t pk[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; i++) { int qi = __float2int_rn(__fmul_rn(v[i], inv)); tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3)); }
+    reinterpret_cast<uint4 *>(aq + (size_t)a * FFN)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (lane == 0) { aqs[a] = s; aqsum[a] = tot; }
+}
+extern "C" void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np) {
+    if (np <= 0) return;
+    silu_quant_kernel<<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np); g_launches++;
+}
+
+// ------------------------------------------------------------------------------------------------------------
 // Combine (maple.c:834): out[b] = init[b] (or 0) then, for the token's pairs in ascending pair order,
 // out = fma(w, down, out) -- the order and the fused rounding of the reference's compiled loop.
 // ------------------------------------------------------------------------------------------------------------

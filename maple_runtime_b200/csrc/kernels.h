@@ -47,6 +47,8 @@ typedef struct {
 } GroupArgs;
 void k_group(cudaStream_t st, const GroupArgs *g);
 void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max);
+/* SiLU*up then per-pair int8 from stored gate and up (the tensor-core path); act may be NULL */
+void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np);
 void k_combine(cudaStream_t st, const float *down, const float *uw, const int *tp, const float *init, float *out, int nb);
 
 /* register-decode + mma.sync grouped kernels (any token count; the decode-batch path); tn = 8 or 32 */

@@ -33,6 +33,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// the same on a shared-memory address held in a register; the first poll is inline so that a completed phase costs one instruction
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, volatile int *abort) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    for (uint32_t i = 0; i < MBAR_SPINS; i++) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*abort) return false;
+        if (i > 1024) __nanosleep(64);
+    }
+    *abort = 1;
+    return false;
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------------------
 // one warp, all lanes: allocates ncols (power of two >= 32) columns, the address lands in *dst (shared memory)
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst, uint32_t ncols) {
@@ -78,6 +93,10 @@ __device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 // the mbarrier gets one arrival when every MMA issued so far by this thread has finished
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // ---- tensor memory <-> registers: thread t of warp w touches lane 32 (w % 4) + t, 32 consecutive columns ------------
