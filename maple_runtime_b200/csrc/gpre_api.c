@@ -21,7 +21,7 @@
 #define MAXREG 64          /* gpu_pre.m:21 */
 #define MAXSYNTH 64
 #define MAP_CACHE 16384
-#define UMMA_TN 80         /* tokens per tile of the tcgen05 kernels (k_expert_umma.cu) */
+#define UMMA_TN 128        /* tokens per tile of the tcgen05 kernels (k_expert_umma.cu) */
 
 static char g_err[512];
 static int fail(const char *who, const char *fmt, ...) {

@@ -1,6 +1,6 @@
 // k_expert_umma.cu -- grouped ternary expert GEMMs on the 5th-generation tensor cores (tcgen05.mma kind::i8), sm_100a.
 //
-// Work item = one tile (a used expert and up to 80 of its pairs) x one block of 2 x 128 weight rows:
+// Work item = one tile (a used expert and up to 128 of its pairs) x one block of 2 x 128 weight rows:
 //   gate+up: 128 gate rows and the 128 up rows of the same index (the SiLU*up epilogue finds both in one thread);
 //   down:    two consecutive blocks of 128 down rows.
 // D[128 rows][N tokens] (s32, tensor memory) += A[128 rows][K] (u8 codes 0,1,2) x B[N tokens][K]^T (s8 activations).
@@ -16,15 +16,18 @@
 //            order; convert.py:29-33) and writes the block with tcgen05.st into the tensor-memory A operand: lane = row,
 //            one 32-bit cell = four consecutive K values.  Decoded weights never touch shared memory;
 //   B        int8 activation rows in pair order (a gather kernel puts the tokens' rows into expert-grouped order first), TMA
-//            tiled copies (box = 128 bytes x 80 rows, 128-byte swizzle = the K-major layout the MMA descriptor names).
+//            tiled copies (box = 128 bytes x 128 rows, 128-byte swizzle = the K-major layout the MMA descriptor names).
+// A pipeline round is two 128-column blocks: the waits and commits of the MMA warps cost about as much as four MMAs each, so
+// they are paid once per eight MMAs.
 // Arithmetic = maple.c:425-458: out = (float)(sum(code*q) - qsum) * qs * s[r]; integer sums are exact.
 //
-// Warps (608 threads): 0-3 decode rows of accumulator 0, 4-7 rows of accumulator 1, 8 weight TMA, 9 B TMA, 10 MMA issue,
-// 11-18 epilogue (two accumulator buffers, so an epilogue overlaps the next item's MMAs).
+// Warps (640 threads): 0-3 decode rows of accumulator 0, 4-7 rows of accumulator 1, 8 weight TMA, 9 B TMA, 10 and 11 MMA issue
+// (one warp per accumulator: a single thread cannot issue tcgen05.mma fast enough to fill the tensor pipe at N <= 80, two can),
+// 12-19 epilogue.
 // Every mbarrier wait is bounded (umma.cuh): on a timeout the CTA raises args.err, frees tensor memory and returns.
 //
-// Tensor memory (512 columns): accumulator buffer b at 160 b (acc 0) and 160 b + 80 (acc 1); A stage s at 320 + 64 s
-// (rows of acc 0) and 352 + 64 s (rows of acc 1).
+// Tensor memory (512 columns): accumulator 0 at 0, accumulator 1 at 128 (N <= 128 columns each); A stage s at 256 + 128 s:
+// rows of accumulator h, block i of the round at + 64 h + 32 i.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -34,17 +37,17 @@
 
 extern "C" void k_count_add(long n);
 
-#define UM_TN 80
-#define UM_ASTAGES 3
-#define UM_WSTAGES 4
-#define UM_BSTAGES 6
+#define UM_TN 128
+#define UM_ASTAGES 2                 /* rounds of two 128-column blocks */
+#define UM_WSTAGES 3
+#define UM_BSTAGES 3                 /* rounds too: 2 x 128 rows x 128 bytes */
 #define UM_WBYTES (256 * 128)
-#define UM_BBYTES (UM_TN * 128)
-#define UM_ACOL 320
+#define UM_BBYTES (2 * UM_TN * 128)
+#define UM_ACOL 256
 
 struct __align__(16) UmShared {
-    uint64_t w_full[UM_WSTAGES], w_empty[UM_WSTAGES], a_full[UM_ASTAGES], a_empty[UM_ASTAGES];
-    uint64_t b_full[UM_BSTAGES], b_empty[UM_BSTAGES], acc_full[2], acc_empty[2];
+    uint64_t w_full[UM_WSTAGES], w_empty[UM_WSTAGES], a_full[2][UM_ASTAGES], a_empty[2][UM_ASTAGES];   // A barriers per accumulator
+    uint64_t b_full[UM_BSTAGES], b_empty[UM_BSTAGES], acc_full, acc_empty;
     uint32_t tmem_base; int abort_flag;
     unsigned long long exp_tab[32];
     float m_qs[8][UM_TN]; int m_qsum[8][UM_TN];      // per epilogue warp: scale and code-sum correction of the tile's tokens
@@ -62,11 +65,11 @@ __device__ long long g_um_trace[32][8];
 #define TWAIT(id, call) (call)
 #endif
 template <int KB, bool GATEUP>
-__global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap bmap) {
+__global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap bmap) {
     extern __shared__ __align__(1024) uint8_t um_smem_raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *wsm = base;                                              // UM_WSTAGES x 32 KB packed weights
-    uint8_t *bsm = base + UM_WSTAGES * UM_WBYTES;                      // UM_BSTAGES x 10 KB int8 activations (1024-aligned: 10240 = 10 x 1024)
+    uint8_t *bsm = base + UM_WSTAGES * UM_WBYTES;                      // UM_BSTAGES x 32 KB int8 activations (two 16 KB blocks per round)
     UmShared *sh = reinterpret_cast<UmShared *>(bsm + UM_BSTAGES * UM_BBYTES);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int MB = GATEUP ? 4 : 8, NSB = KB / 4;
@@ -75,9 +78,9 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
 
     if (tid == 0) {
         for (int s = 0; s < UM_WSTAGES; s++) { mbar_init(&sh->w_full[s], 1); mbar_init(&sh->w_empty[s], 8); }
-        for (int s = 0; s < UM_ASTAGES; s++) { mbar_init(&sh->a_full[s], 8); mbar_init(&sh->a_empty[s], 1); }
-        for (int s = 0; s < UM_BSTAGES; s++) { mbar_init(&sh->b_full[s], 1); mbar_init(&sh->b_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&sh->acc_full[s], 1); mbar_init(&sh->acc_empty[s], 8); }
+        for (int s = 0; s < UM_ASTAGES; s++) for (int h = 0; h < 2; h++) { mbar_init(&sh->a_full[h][s], 4); mbar_init(&sh->a_empty[h][s], 1); }
+        for (int s = 0; s < UM_BSTAGES; s++) { mbar_init(&sh->b_full[s], 1); mbar_init(&sh->b_empty[s], 2); }
+        mbar_init(&sh->acc_full, 2); mbar_init(&sh->acc_empty, 8);
         sh->abort_flag = 0; mbar_init_fence();
     }
     if (tid < 32) sh->exp_tab[tid] = DEV_EXP_TAB[tid];
@@ -94,7 +97,7 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
     if (warp < 8) {
         // ---------------- decode: one weight row per thread, packed bytes from the shared-memory ring ----------------
         const int h = warp >> 2, R = h * 128 + (warp & 3) * 32 + lane;
-        const uint32_t a_lane = tb + ((uint32_t)((warp & 3) * 32) << 16) + UM_ACOL + h * 32;
+        const uint32_t a_lane = tb + ((uint32_t)((warp & 3) * 32) << 16) + UM_ACOL + h * 64;
         uint32_t wcnt = 0, acnt = 0;
         for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
 #pragma unroll 1
@@ -103,23 +106,28 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
                 if (!TWAIT(0, mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp))) { live = false; break; }
                 const uint8_t *wr = wsm + ws * UM_WBYTES + R * 128;
 #pragma unroll
-                for (int q = 0; q < 4; q++, acnt++) {
-                    const uint4 v0 = *reinterpret_cast<const uint4 *>(wr + (((2 * q) ^ (R & 7)) << 4));
-                    const uint4 v1 = *reinterpret_cast<const uint4 *>(wr + (((2 * q + 1) ^ (R & 7)) << 4));
-                    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                    uint32_t r[32];
-#pragma unroll
-                    for (int sft = 0; sft < 4; sft++)
-#pragma unroll
-                        for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
+                for (int rd = 0; rd < 2; rd++, acnt++) {                 // two rounds per weight stage, two 128-column blocks per round
                     const int as = acnt % UM_ASTAGES;
-                    if (!TWAIT(1, mbar_wait(&sh->a_empty[as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp))) { live = false; break; }
+                    uint32_t r[32];
+                    auto decode = [&](int q) {
+                        const uint4 v0 = *reinterpret_cast<const uint4 *>(wr + (((2 * q) ^ (R & 7)) << 4));
+                        const uint4 v1 = *reinterpret_cast<const uint4 *>(wr + (((2 * q + 1) ^ (R & 7)) << 4));
+                        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                        for (int sft = 0; sft < 4; sft++)
+#pragma unroll
+                            for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
+                    };
+                    decode(2 * rd);                                      // the first block is ready before the stage is free
+                    if (!TWAIT(1, mbar_wait(&sh->a_empty[h][as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     tc_fence_after();
-                    tmem_st32(a_lane + as * 64, r);
+                    tmem_st32(a_lane + as * 128, r);
+                    decode(2 * rd + 1);
+                    tmem_st32(a_lane + as * 128 + 32, r);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->a_full[as]);
+                    if (lane == 0) mbar_arrive(&sh->a_full[h][as]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->w_empty[ws]);
@@ -149,56 +157,61 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
             }
         }
     } else if (warp == 9) {
-        // ---------------- B TMA (one lane): 80 rows x 128 bytes of the pair-ordered int8 activations per stage ----------------
+        // ---------------- B TMA (one lane): per round two boxes of 128 rows x 128 bytes of the pair-ordered int8 activations ----------------
         if (lane == 0) {
             uint32_t bcnt = 0;
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
                 const MoeTile tile = a.tiles[item / MB];
-                for (int kb = 0; kb < KB && live; kb++, bcnt++) {
+                for (int kb = 0; kb < KB && live; kb += 2, bcnt++) {
                     const int s = bcnt % UM_BSTAGES;
                     if (!TWAIT(0, mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     mbar_expect_tx(&sh->b_full[s], UM_BBYTES);
                     tma_load_2d(smem_u32(bsm + s * UM_BBYTES), &bmap, kb * 128, tile.p0, &sh->b_full[s]);
+                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES + UM_TN * 128), &bmap, kb * 128 + 128, tile.p0, &sh->b_full[s]);
                 }
             }
         }
-    } else if (warp == 10) {
-        // ---------------- MMA issue (one lane).  Stage indices and parities are carried in registers (wrap by compare, no
-        // division), descriptors and column addresses are base + stage * constant: the thread's instructions go to the MMAs ----------------
+    } else if (warp < 12) {
+        // ---------------- MMA issue: warp 10 accumulator 0, warp 11 accumulator 1 (one lane each).  Stage indices and parities are
+        // carried in registers (wrap by compare), descriptors and column addresses are base + stage * constant ----------------
         if (lane == 0) {
+            const int h = warp - 10;
             const uint64_t bdesc0 = smem_desc_k128(smem_u32(bsm), 0);
-            const uint32_t afull0 = smem_u32(&sh->a_full[0]), aempty0 = smem_u32(&sh->a_empty[0]);
+            const uint32_t afull0 = smem_u32(&sh->a_full[h][0]), aempty0 = smem_u32(&sh->a_empty[h][0]);
             const uint32_t bfull0 = smem_u32(&sh->b_full[0]), bempty0 = smem_u32(&sh->b_empty[0]);
             uint32_t as = 0, ap = 0, bs = 0, bp = 0, icnt = 0;
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
                 const MoeTile tile = a.tiles[item / MB];
                 const uint32_t idesc = idesc_i8_u8s8((uint32_t)((tile.cnt + 15) & ~15));
-                const int buf = icnt & 1;
-                if (!TWAIT(0, mbar_wait(&sh->acc_empty[buf], ((icnt >> 1) & 1) ^ 1, abortp))) { live = false; break; }
+                if (!TWAIT(0, mbar_wait(&sh->acc_empty, (icnt & 1) ^ 1, abortp))) { live = false; break; }
                 tc_fence_after();
-                const uint32_t d0 = tb + buf * 160, d1 = d0 + 80;
+                const uint32_t d = tb + h * 128;
 #pragma unroll 1
-                for (int kb = 0; kb < KB; kb++) {
+                for (int kb = 0; kb < KB; kb += 2) {
                     if (!TWAIT(1, mbar_wait_addr(afull0 + as * 8, ap, abortp)) || !TWAIT(2, mbar_wait_addr(bfull0 + bs * 8, bp, abortp))) { live = false; break; }
                     tc_fence_after();
-                    const uint32_t acol = tb + UM_ACOL + as * 64;
+                    const uint32_t acol = tb + UM_ACOL + as * 128 + h * 64;
                     const uint64_t bd = bdesc0 + (uint64_t)(bs * (UM_BBYTES >> 4));
-                    const uint32_t acc = kb != 0;
-                    umma_i8_ts(d0, acol, bd, idesc, acc);          umma_i8_ts(d1, acol + 32, bd, idesc, acc);
-                    umma_i8_ts(d0, acol + 8, bd + 2, idesc, 1);    umma_i8_ts(d1, acol + 40, bd + 2, idesc, 1);
-                    umma_i8_ts(d0, acol + 16, bd + 4, idesc, 1);   umma_i8_ts(d1, acol + 48, bd + 4, idesc, 1);
-                    umma_i8_ts(d0, acol + 24, bd + 6, idesc, 1);   umma_i8_ts(d1, acol + 56, bd + 6, idesc, 1);
+                    umma_i8_ts(d, acol, bd, idesc, kb != 0);
+                    umma_i8_ts(d, acol + 8, bd + 2, idesc, 1);
+                    umma_i8_ts(d, acol + 16, bd + 4, idesc, 1);
+                    umma_i8_ts(d, acol + 24, bd + 6, idesc, 1);
+                    const uint64_t bd1 = bd + (UM_TN * 128 >> 4);
+                    umma_i8_ts(d, acol + 32, bd1, idesc, 1);
+                    umma_i8_ts(d, acol + 40, bd1 + 2, idesc, 1);
+                    umma_i8_ts(d, acol + 48, bd1 + 4, idesc, 1);
+                    umma_i8_ts(d, acol + 56, bd1 + 6, idesc, 1);
                     umma_commit_addr(aempty0 + as * 8);
                     umma_commit_addr(bempty0 + bs * 8);
                     if (++as == UM_ASTAGES) { as = 0; ap ^= 1; }
                     if (++bs == UM_BSTAGES) { bs = 0; bp ^= 1; }
                 }
-                if (live) umma_commit(&sh->acc_full[buf]);
+                if (live) umma_commit(&sh->acc_full);
             }
         }
     } else {
-        // ---------------- epilogue: lane = weight row, columns = tokens; warps 11-14 take the even 16-column pieces, 15-18 the odd ----------------
-        const int ew = warp - 11, q4 = warp & 3, half = ew >> 2, row = q4 * 32 + lane;   // a warp reaches the tensor-memory lanes 32 (warp % 4) ..
+        // ---------------- epilogue: lane = weight row, columns = tokens; warps 12-15 take the even 16-column pieces, 16-19 the odd ----------------
+        const int ew = warp - 12, q4 = warp & 3, half = ew >> 2, row = q4 * 32 + lane;   // a warp reaches the tensor-memory lanes 32 (warp % 4) ..
         uint32_t icnt = 0;
         for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
             const MoeTile tile = a.tiles[item / MB];
@@ -206,26 +219,25 @@ __global__ void __launch_bounds__(608, 1) expert_umma_kernel(ExpertArgs a, const
             const ExpertPtrs ep = a.tab[ex];
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
             const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
-            const int buf = icnt & 1;
             __syncwarp();
             for (int n = lane; n < N; n += 32) {
                 const int pair = tile.p0 + (n < cnt ? n : 0), t = GATEUP ? a.ptok[pair] : pair;
                 sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
             }
             __syncwarp();
-            if (!TWAIT(0, mbar_wait(&sh->acc_full[buf], (icnt >> 1) & 1, abortp))) { live = false; break; }
+            if (!TWAIT(0, mbar_wait(&sh->acc_full, icnt & 1, abortp))) { live = false; break; }
             tc_fence_after();
-            const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16) + buf * 160;
+            const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16);
             const int c_last = ((N / 16 - 1 - half) & ~1) + half;           // this warp's last piece (negative: none)
-            if (half * 16 >= N) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->acc_empty[buf]); }
+            if (half * 16 >= N) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->acc_empty); }
             for (int c0 = half * 16; c0 < N; c0 += 32) {
                 uint32_t v0[16], v1[16];
-                tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 80 + c0, v1);
+                tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 128 + c0, v1);
                 tmem_ld_wait();
                 if (c0 == c_last * 16) {   // the buffer is in registers: hand it back before the arithmetic
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+                    if (lane == 0) mbar_arrive(&sh->acc_empty);
                 }
                 float o0[16], o1[16];
 #pragma unroll
@@ -274,7 +286,7 @@ static void launch(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) {
         int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         cudaFuncSetAttribute(expert_umma_kernel<KB, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    expert_umma_kernel<KB, GATEUP><<<sms, 608, smem, st>>>(*a, *bmap);
+    expert_umma_kernel<KB, GATEUP><<<sms, 640, smem, st>>>(*a, *bmap);
     k_count_add(1);
 }
 extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) { if (a->max_tiles > 0) launch<16, true>(st, a, bmap); }

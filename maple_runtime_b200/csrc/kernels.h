@@ -55,8 +55,8 @@ void k_combine(cudaStream_t st, const float *down, const float *uw, const int *t
 void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 
-/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 80 tokens, codes decoded in registers into tensor memory */
-/* bmap: tensor map over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down), box 128 x 80 */
+/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */
+/* bmap: tensor map over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down), box 128 x 128 */
 void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
 void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
