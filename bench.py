@@ -83,8 +83,16 @@ def init_dist(world):
         return None
     import torch.distributed as dist
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    dist.init_process_group("gloo")   # plumbing only: barrier and max over ranks of device-measured times
+    dist.init_process_group("gloo")   # plumbing only: hands the NCCL id and the CUDA IPC handles to the ranks, host barriers
     return dist
+
+
+def gather_obj(dist):
+    def f(obj):
+        out = [None] * dist.get_world_size()
+        dist.all_gather_object(out, obj)
+        return out
+    return f
 
 
 def allmax(dist, v):
@@ -152,7 +160,8 @@ def reference_main(args, rank, world):
 def workload_config(world):
     return {"workload": "24-layer Maple MoE stack (d=2048, 256 ternary experts 512/2048, top-8), prefill chunk of 2048 tokens per GPU, "
                         "hidden ~N(0,1), random router (near-uniform routing), seeded synthetic weights",
-            "tokens_per_step_per_gpu": NB, "layers": LAYERS, "parallelism": "replicas" if world > 1 else "single",
+            "tokens_per_step_per_gpu": NB, "layers": LAYERS,
+            "parallelism": f"ep{world}: tokens split over the GPUs, {256 // world} experts per GPU, dispatch and combine by peer stores over NVLink" if world > 1 else "single",
             "l2": "inputs larger than L2: 4.9 GB of expert weights are streamed from HBM every step"}
 
 
@@ -177,8 +186,21 @@ def main():
     g = ml.Gpre(NB, device=local)
     clib = g.lib
     nl = args.layers
+    epr = 256 // world
     for L in range(nl):
-        g.synth_layer(SEED, L)
+        g.synth_layer(SEED, L, rank * epr, epr)        # expert parallel: each GPU holds only its own experts
+    if world > 1:
+        from maple_runtime_b200 import ep
+        ep.setup(g, rank, world, gather_obj(dist))
+
+    def forward_chunk(c):
+        if world > 1:
+            g._chk(clib.gmoe_ep_forward_dev(c, NB, 0, nl, None))
+        else:
+            g._chk(clib.gmoe_forward_chunk(c, NB, 0, nl, None))
+
+    def forward_host(ptr):
+        return g._chk(clib.gmoe_ep_forward(ptr, NB, 0, nl, None) if world > 1 else clib.gmoe_forward(ptr, NB, 0, nl, None))
     nring = 4
     ring = np.concatenate([ml.synth_hidden(clib, SEED, 2000 + rank * 16 + c, NB) for c in range(nring)])
     g._chk(clib.gmoe_chunks_upload(ring.ctypes.data, NB, nring))
@@ -187,7 +209,7 @@ def main():
     import ctypes as C
     ev_total = []
     for i in range(warm):
-        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None)); g._chk(clib.gmoe_sync())
+        forward_chunk(i % nring); g._chk(clib.gmoe_sync())
     sampler = ClockSampler(local); sampler.start()
     g.profile(1 << 4)                                  # events around the gate+up launches only
     l0 = clib.gmoe_launch_count()
@@ -195,7 +217,7 @@ def main():
     t_dev = 0.0
     wall0 = time.perf_counter()
     for i in range(args.steps):
-        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None))
+        forward_chunk(i % nring)
         t_dev += g._chk(clib.gmoe_sync())              # device seconds of this step (events on the library's stream)
     wall = time.perf_counter() - wall0
     barrier(dist)
@@ -209,7 +231,7 @@ def main():
     # ---- stage breakdown (separate pass, all stages timed) ----
     g.profile(0xFF)
     for i in range(2):
-        g._chk(clib.gmoe_forward_chunk(i % nring, NB, 0, nl, None))
+        forward_chunk(i % nring)
     st_secs, st_n = g.profile_read()
     g.profile(0)
     breakdown = {name: round(float(s) / (2 * nl) * 1e6, 2) for name, s in zip(g.STAGES, st_secs)}   # us per layer
@@ -222,7 +244,7 @@ def main():
         hbuf[:] = ring[(i % nring) * NB:(i % nring + 1) * NB]
         if i == warm:
             barrier(dist)
-        t = g._chk(clib.gmoe_forward(hx, NB, 0, nl, None))
+        t = forward_host(hx)
         if i >= warm:
             t_e2e += t
     barrier(dist)
@@ -231,7 +253,7 @@ def main():
 
     # ---- roofline of the dominant kernel ----
     pk = peaks()
-    gu_t = float(secs[4]) / max(int(nlaunch[4]), 1)
+    gu_t = float(secs[4]) / max(int(nlaunch[4]), 1)          # stage 4 is one launch per layer: the grouped gate+up GEMM
     gu_tops = GU_OPS_PER_PAIR * NB * 8 / gu_t / 1e12
     int8_peak = 2.0 * pk["bf16_tflops_sustained"]
     roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary)", "bound": "tensor", "achieved": gu_tops, "peak": int8_peak, "unit": "TOP/s (int8)",
@@ -250,9 +272,11 @@ def main():
         out["note"] = "reduced layer count: a profiling run, not a benchmark number"
 
     # ---- decode shape: 64 conversations x 1 token, one layer at a time over all layers (HBM-bound) ----
-    if not args.no_decode and rank == 0:
+    if world > 1:
+        out["ep_received_pairs_last_layer"] = [int(v) for v in gather_obj(dist)(clib.gmoe_ep_received())]
+    if not args.no_decode and rank == 0 and world == 1:
         out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
-    if not args.no_cpu and rank == 0 and world >= 1:
+    if not args.no_cpu and rank == 0:
         _, _, out["cpu_baseline"] = cpu_reference_arm(8, 1, as_baseline=True)
     if rank == 0:
         print(json.dumps(out))

@@ -39,13 +39,13 @@ const char *gmoe_last_error(void) { return g_err; }
 typedef struct { uint16_t *router, *post_ln; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
 
 static struct {
-    int ready, maxtok, maxp, mask_words, keep, path, nb_cur;
+    int ready, maxtok, maxp, mask_words, keep, path, nb_cur, ep_on;
     cudaStream_t st; cudaEvent_t e0, e1;
     void *reg[MAXREG]; size_t reg_len[MAXREG]; int nreg; double blit_s;
     LayerDev ly[GMOE_LAYERS];
     float *x, *hn, *y, *hqs, *logits, *topw, *uw, *act, *aqs, *down, *gate, *up, *bias;
     int8_t *hq, *aq;
-    int *hqsum, *top, *nu, *ue, *estart, *ustart, *utok, *slot, *tp, *aqsum, *ntiles_a, *ntiles_b, *gu_dots, *dn_dots;
+    int *ecnt, *uexp, *hqsum, *top, *nu, *ue, *estart, *ustart, *utok, *slot, *tp, *aqsum, *ntiles_a, *ntiles_b, *gu_dots, *dn_dots;
     unsigned *mask; int *err, *h_err;
     MoeTile *tiles_a, *tiles_b;
     ExpertPtrs *tab_call;      /* the used experts of one gpre_moe call */
@@ -106,6 +106,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(x, T * HID * 4); ALLOC(hn, T * HID * 4); ALLOC(y, T * HID * 4);
     ALLOC(hq, T * HID); ALLOC(hqs, T * 4); ALLOC(hqsum, T * 4);
     ALLOC(logits, T * NEXP * 4); ALLOC(top, P * 4); ALLOC(topw, P * 4); ALLOC(bias, NEXP * 4);
+    ALLOC(ecnt, NEXP * 4); ALLOC(uexp, P * 4);
     ALLOC(mask, (size_t)NEXP * S.mask_words * 4); ALLOC(nu, 16); ALLOC(ue, NEXP * 4); ALLOC(estart, NEXP * 4);
     ALLOC(ustart, (NEXP + 1) * 4); ALLOC(utok, P * 4); ALLOC(uw, P * 4); ALLOC(slot, P * 4); ALLOC(tp, P * 4);
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
@@ -285,9 +286,12 @@ static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const ExpertM
     if (S.keep) { a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
 }
 static void run_group(int nb) {
-    GroupArgs g = {S.top, S.topw, nb, S.mask, S.mask_words, S.nu, S.ue, S.estart, S.ustart, S.utok, S.slot, S.tp, S.uw,
-                   S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tile_tn(nb), UMMA_TN};
+    GroupArgs g; memset(&g, 0, sizeof g);
+    g.top = S.top; g.topw = S.topw; g.nb = nb; g.mask = S.mask; g.mask_words = S.mask_words; g.nu = S.nu; g.ue = S.ue; g.estart = S.estart;
+    g.ustart = S.ustart; g.utok = S.utok; g.slot = S.slot; g.tp = S.tp; g.uw = S.uw; g.ecnt = S.ecnt; g.uexp = S.uexp;
+    g.tiles_a = S.tiles_a; g.tiles_b = S.tiles_b; g.ntiles_a = S.ntiles_a; g.ntiles_b = S.ntiles_b; g.tn_a = tile_tn(nb); g.tn_b = UMMA_TN;
     k_group(S.st, &g);
+    if (use_umma(nb) && !S.ep_on) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);   /* the permute: int8 rows into pair order for the TMA */
 }
 static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
     ExpertArgs a; fill_expert_args(&a, tab, maps, ue, nb);
@@ -295,12 +299,12 @@ static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int
     int um = use_umma(nb);
     if (which & 1) {
         prof_begin(4);
-        if (um) { k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); k_gateup_umma(S.st, &a, &S.bmap_hq); } else k_gateup_mma(S.st, &a, tn);
+        if (um) k_gateup_umma(S.st, &a, &S.bmap_hq); else k_gateup_mma(S.st, &a, tn);
         prof_end(4);
     }
     if (which & 2) {
         prof_begin(5);
-        if (um) k_silu_quant(S.st, S.gate, S.up, S.keep ? S.act : NULL, S.aq, S.aqs, S.aqsum, nb * TOPK);
+        if (um) k_silu_quant(S.st, S.gate, S.up, S.keep ? S.act : NULL, S.aq, S.aqs, S.aqsum, nb * TOPK, NULL);
         else k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK);
         prof_end(5);
     }
@@ -463,6 +467,7 @@ double gpre_moe(const float *x, int nb, int nu, const uint32_t *loc, const int *
     CUD("gpre", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
     cudaEventRecord(S.e0, S.st);
     k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
+    if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);
     run_experts(S.tab_call, S.maps_call, NULL, nb, 7);
     k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
     cudaEventRecord(S.e1, S.st);
@@ -479,6 +484,7 @@ void gfull_moe(int nu, const uint32_t *loc, const int *regs, const int *ustart, 
     int nb = S.nb_cur;
     if (upload_grouping("gfull", nb, nu, loc, regs, ustart, ptok, pw, tp)) return;
     cudaEventRecord(S.e0, S.st);
+    if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);
     run_experts(S.tab_call, S.maps_call, NULL, nb, 7);            /* hq/hqs/hqsum were left by gmoe_post_norm */
     k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
     cudaEventRecord(S.e1, S.st);
@@ -538,7 +544,7 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "router_bias")) k_router_logits(S.st, l->router, S.hn, S.bias, S.logits, nb);
     else if (!strcmp(name, "topk")) k_topk(S.st, S.logits, S.top, S.topw, nb);
     else if (!strcmp(name, "group")) run_group(nb);
-    else if (!strcmp(name, "gateup")) run_experts(l->tab, l->maps, S.ue, nb, 1);
+    else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, S.ue, nb, 1); }
     else if (!strcmp(name, "actq")) run_experts(l->tab, l->maps, S.ue, nb, 2);
     else if (!strcmp(name, "down")) run_experts(l->tab, l->maps, S.ue, nb, 4);
     else if (!strcmp(name, "combine_y")) k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
@@ -592,3 +598,163 @@ void *gpux_begin_multi(int L, const float *x, int nb, int nu, const int *slots, 
     (void)L; (void)x; (void)nb; (void)nu; (void)slots; (void)pstart; (void)ptok; return NULL;
 }
 void gpux_end_multi(void *h, float *out, int np) { (void)h; (void)out; (void)np; }
+
+/* ================================================================================================================
+ * Expert parallelism across the GPUs of one NVLink box (one process per GPU).  The reference has no counterpart
+ * (single process, single device).  Rank r keeps its own tokens and the experts r*E .. (r+1)*E-1, E = 256 / world.
+ * Per layer: local norm / router / top-8 / grouping -> all-gather of the per-expert pair counts (NCCL) -> every rank
+ * stores its int8 rows straight into the owners' receive buffers (k_ep.cu, peer stores over NVLink) -> barrier ->
+ * the owners run gate+up, SiLU+int8 and down on what they received, the down epilogue stores each result row
+ * straight into the token's rank -> barrier -> local combine, in the same order as on one GPU, so the hidden state
+ * is the same bits as without expert parallelism.  NCCL carries only the 1 KB count exchange and the barriers.
+ * ================================================================================================================ */
+#include <dlfcn.h>
+#include <nccl.h>
+
+static struct {
+    int rank, world, epr; size_t rcap;
+    void *lib; ncclComm_t comm;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    const char *(*GetErrorString)(ncclResult_t);
+    int *all_cnt, *dst_base, *total, *nu_r, *ue_r, *ustart_r, *rx_qsum; float *rx_qs; int2 *rx_src; double *red;
+    void *peer[5][8];                       /* opened buffers of every rank: rx rows, rx scales, rx sums, rx return addresses, down rows */
+    void **peer_dev[5];                     /* the same tables in device memory */
+} EP;
+
+static int ep_nccl(const char *who) {
+    if (EP.lib) return 0;
+    EP.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!EP.lib) return fail(who, "libnccl.so.2 cannot be loaded: %s", dlerror());
+#define SYM(field, name) do { *(void **)&EP.field = dlsym(EP.lib, name); if (!EP.field) return fail(who, "libnccl has no %s", name); } while (0)
+    SYM(GetUniqueId, "ncclGetUniqueId"); SYM(CommInitRank, "ncclCommInitRank"); SYM(AllGather, "ncclAllGather");
+    SYM(AllReduce, "ncclAllReduce"); SYM(GetErrorString, "ncclGetErrorString");
+#undef SYM
+    return 0;
+}
+#define NC(who, call) do { ncclResult_t r_ = (call); if (r_ != ncclSuccess) return fail(who, "%s: %s", #call, EP.GetErrorString(r_)); } while (0)
+
+int gmoe_ep_unique_id(void *out128) {
+    if (ep_nccl("gmoe")) return -1;
+    ncclUniqueId id; NC("gmoe", EP.GetUniqueId(&id)); memcpy(out128, &id, sizeof id); return 0;
+}
+#define EP_REALLOC(field, bytes) do { cudaFree(S.field); S.field = NULL; if (dmalloc((void **)&S.field, (bytes))) return fail("gmoe", "expert parallel: no device memory for %s", #field); } while (0)
+#define EP_ALLOC(field, bytes) do { if (dmalloc((void **)&EP.field, (bytes))) return fail("gmoe", "expert parallel: no device memory for %s", #field); } while (0)
+int gmoe_ep_init(int rank, int world, const void *id128) {
+    if (!S.ready) return fail("gmoe", "gmoe_ep_init before gmoe_init");
+    if (S.ep_on) return fail("gmoe", "expert parallelism is already set up");
+    if (world < 1 || world > 8 || (NEXP % world) || rank < 0 || rank >= world) return fail("gmoe", "rank %d of %d", rank, world);
+    if (ep_nccl("gmoe")) return -1;
+    ncclUniqueId id; memcpy(&id, id128, sizeof id);
+    NC("gmoe", EP.CommInitRank(&EP.comm, world, id, rank));
+    EP.rank = rank; EP.world = world; EP.epr = NEXP / world; EP.rcap = (size_t)world * S.maxp;
+    const size_t R = EP.rcap;
+    /* everything indexed by received pairs grows to the worst case: every pair of every rank lands here */
+    EP_REALLOC(hq_sorted, R * HID); EP_REALLOC(gate, R * FFN * 4); EP_REALLOC(up, R * FFN * 4); EP_REALLOC(act, R * FFN * 4);
+    EP_REALLOC(aq, R * FFN); EP_REALLOC(aqs, R * 4); EP_REALLOC(aqsum, R * 4);
+    EP_REALLOC(tiles_a, (R / 8 + NEXP) * sizeof(MoeTile)); EP_REALLOC(tiles_b, (R / 8 + NEXP) * sizeof(MoeTile));
+    if (S.gu_dots) { EP_REALLOC(gu_dots, R * 2 * FFN * 4); EP_REALLOC(dn_dots, R * HID * 4); }
+    if (tmap_bytes_2d("gmoe", &S.bmap_hq, S.hq_sorted, HID, R, HID, 128, UMMA_TN) || tmap_bytes_2d("gmoe", &S.bmap_aq, S.aq, FFN, R, FFN, 128, UMMA_TN)) return -1;
+    EP_ALLOC(all_cnt, (size_t)world * NEXP * 4); EP_ALLOC(dst_base, NEXP * 4); EP_ALLOC(total, 16); EP_ALLOC(nu_r, 16); EP_ALLOC(ue_r, NEXP * 4);
+    EP_ALLOC(ustart_r, (NEXP + 1) * 4); EP_ALLOC(rx_qs, R * 4); EP_ALLOC(rx_qsum, R * 4); EP_ALLOC(rx_src, R * sizeof(int2)); EP_ALLOC(red, 64);
+    for (int k = 0; k < 5; k++) if (dmalloc((void **)&EP.peer_dev[k], 8 * sizeof(void *))) return fail("gmoe", "expert parallel: no device memory");
+    S.ep_on = 1;
+    return 0;
+}
+/* 5 x 64 bytes: the handles other ranks need to store into this rank's buffers */
+int gmoe_ep_handles(void *out320) {
+    if (!S.ep_on) return fail("gmoe", "gmoe_ep_handles before gmoe_ep_init");
+    void *p[5] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down};
+    for (int k = 0; k < 5; k++) CU("gmoe", cudaIpcGetMemHandle((cudaIpcMemHandle_t *)((char *)out320 + 64 * k), p[k]));
+    return 0;
+}
+/* all: world x 5 x 64 bytes, rank-major, as gathered from gmoe_ep_handles */
+int gmoe_ep_connect(const void *all) {
+    if (!S.ep_on) return fail("gmoe", "gmoe_ep_connect before gmoe_ep_init");
+    void *mine[5] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down};
+    for (int r = 0; r < EP.world; r++) for (int k = 0; k < 5; k++) {
+        if (r == EP.rank) { EP.peer[k][r] = mine[k]; continue; }
+        cudaIpcMemHandle_t h; memcpy(&h, (const char *)all + ((size_t)r * 5 + k) * 64, 64);
+        CU("gmoe", cudaIpcOpenMemHandle(&EP.peer[k][r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    for (int k = 0; k < 5; k++) CU("gmoe", cudaMemcpy(EP.peer_dev[k], EP.peer[k], 8 * sizeof(void *), cudaMemcpyHostToDevice));
+    return 0;
+}
+static int ep_barrier(void) {   /* every rank's earlier work on its stream is complete before any rank's later work starts */
+    NC("gmoe", EP.AllReduce(EP.red, EP.red + 1, 1, ncclDouble, ncclSum, EP.comm, S.st)); return 0;
+}
+static int run_layer_ep(int L, int nb, const float *bias) {
+    LayerDev *l = &S.ly[L];
+    const int tn = tile_tn(nb), um = use_umma(nb);
+    prof_begin(0); k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
+    prof_begin(1); k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb); prof_end(1);
+    prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    prof_begin(3);
+    run_group(nb);
+    NC("gmoe", EP.AllGather(S.ecnt, EP.all_cnt, NEXP, ncclInt, EP.comm, S.st));
+    EpPlanArgs p = {EP.all_cnt, EP.rank, EP.world, EP.dst_base, EP.nu_r, EP.ue_r, EP.ustart_r, EP.total, S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tn, UMMA_TN};
+    k_ep_plan(S.st, &p);
+    EpDispatchArgs d = {S.hq, S.hqs, S.hqsum, S.utok, S.uexp, S.estart, EP.dst_base, nb * TOPK, EP.rank, EP.epr,
+                        (int8_t *const *)EP.peer_dev[0], (float *const *)EP.peer_dev[1], (int *const *)EP.peer_dev[2], (int2 *const *)EP.peer_dev[3]};
+    k_ep_dispatch(S.st, &d);
+    if (ep_barrier()) return -1;
+    prof_end(3);
+    ExpertArgs a; memset(&a, 0, sizeof a);
+    a.tab = l->tab; a.maps = l->maps; a.ue = EP.ue_r; a.err = S.err; a.ptok = NULL;
+    a.tiles = um ? S.tiles_b : S.tiles_a; a.ntiles = um ? S.ntiles_b : S.ntiles_a; a.max_tiles = (int)(EP.rcap / (um ? UMMA_TN : tn)) + NEXP;
+    a.hq = S.hq_sorted; a.hqs = EP.rx_qs; a.hqsum = EP.rx_qsum; a.act = S.act; a.aq = S.aq; a.aqs = S.aqs; a.aqsum = S.aqsum; a.down = S.down;
+    a.rx_src = EP.rx_src; a.peer_down = (float *const *)EP.peer_dev[4];
+    if (S.keep || um) { a.gate = S.gate; a.up = S.up; }
+    if (S.keep) { a.gu_dots = S.gu_dots; a.dn_dots = S.dn_dots; }
+    prof_begin(4); if (um) k_gateup_umma(S.st, &a, &S.bmap_hq); else k_gateup_mma(S.st, &a, tn); prof_end(4);
+    prof_begin(5);
+    if (um) k_silu_quant(S.st, S.gate, S.up, S.keep ? S.act : NULL, S.aq, S.aqs, S.aqsum, (int)EP.rcap, EP.total);
+    else k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, EP.total, (int)EP.rcap);
+    prof_end(5);
+    prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6);
+    prof_begin(7);
+    if (ep_barrier()) return -1;
+    k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
+    prof_end(7);
+    return 0;
+}
+/* The residual stream of this rank's nb tokens through layers l0 .. l0+nl-1, experts sharded over the ranks.
+ * Device-resident form (gmoe_x_upload / gmoe_x_download, gmoe_chunks_upload); asynchronous; every rank calls it with the same nb. */
+int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
+    if (!S.ep_on) return fail("gmoe", "expert parallelism is not set up");
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1;
+    const float *bd = bias_dev(bias);
+    cudaEventRecord(S.e0, S.st);
+    if (chunk >= 0) {
+        if (!S.ring || nb != S.ring_nb || chunk >= S.ring_n) return fail("gmoe", "chunk %d of %d tokens is not in the ring", chunk, nb);
+        cudaMemcpyAsync(S.x, S.ring + (size_t)chunk * nb * HID, (size_t)nb * HID * 4, cudaMemcpyDeviceToDevice, S.st);
+    }
+    for (int L = l0; L < l0 + nl; L++) if (run_layer_ep(L, nb, bd)) return -1;
+    cudaEventRecord(S.e1, S.st);
+    S.nb_cur = nb; return 0;
+}
+/* Host in/out, like gmoe_forward. */
+double gmoe_ep_forward(float *x, int nb, int l0, int nl, const float *bias) {
+    if (!S.ep_on) { fail("gmoe", "expert parallelism is not set up"); return -1.0; }
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1.0;
+    const float *bd = bias_dev(bias);
+    cudaEventRecord(S.e0, S.st);
+    CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
+    for (int L = l0; L < l0 + nl; L++) if (run_layer_ep(L, nb, bd)) return -1.0;
+    CUD("gmoe", cudaMemcpyAsync(x, S.x, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
+    cudaEventRecord(S.e1, S.st);
+    S.nb_cur = nb;
+    return finish("gmoe");
+}
+/* max over ranks of a host value (the benchmark's device-measured seconds), and with it a barrier: NCCL on the library's stream */
+int gmoe_ep_allmax(double *v) {
+    if (!S.ep_on) return fail("gmoe", "expert parallelism is not set up");
+    CU("gmoe", cudaMemcpyAsync(EP.red + 2, v, 8, cudaMemcpyHostToDevice, S.st));
+    NC("gmoe", EP.AllReduce(EP.red + 2, EP.red + 3, 1, ncclDouble, ncclMax, EP.comm, S.st));
+    CU("gmoe", cudaMemcpyAsync(v, EP.red + 3, 8, cudaMemcpyDeviceToHost, S.st));
+    CU("gmoe", cudaStreamSynchronize(S.st)); return 0;
+}
+/* received pairs of the last layer on this rank (load balance report) */
+int gmoe_ep_received(void) { int t = -1; if (S.ep_on) { cudaMemcpyAsync(&t, EP.total, 4, cudaMemcpyDeviceToHost, S.st); cudaStreamSynchronize(S.st); } return t; }

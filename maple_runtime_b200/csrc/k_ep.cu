@@ -1,0 +1,67 @@
+// k_ep.cu -- expert parallelism over one NVLink box: who sends which pairs where (plan), and the dispatch itself.
+//
+// Rank r keeps tokens r*T .. (r+1)*T-1 and the experts r*E .. (r+1)*E-1 (E = 256 / world).  Its pairs are grouped by
+// global expert id (the same grouping as on one GPU), so the pairs for one destination rank are one contiguous run.
+// After an all-gather of the per-expert pair counts every rank can compute, without further communication, where each
+// of its pairs lands in the owner's receive buffer: the owner's pairs are ordered by (expert, source rank, source
+// order), i.e. global token order inside an expert.  The dispatch kernel then stores the int8 activation rows and their
+// scales straight into the owners' buffers over NVLink (plain peer stores, no multicast, no TMA on peer memory), and the
+// owners' down kernels store their result rows straight back into the token's rank (k_expert_*.cu).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "kernels.h"
+
+extern "C" void k_count_add(long n);
+#define NEXP 256
+
+// one CTA, thread e = global expert
+__global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p) {
+    __shared__ int s_tot[NEXP], w_sum[8][4];
+    const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
+    const int epr = NEXP / p.world, owner = e / epr, mine = owner == p.rank;
+    int tot = 0, before = 0;
+    for (int s = 0; s < p.world; s++) { int c = p.all_cnt[s * NEXP + e]; if (s < p.rank) before += c; tot += c; }
+    s_tot[e] = tot;
+    __syncthreads();
+    // offset of expert e inside its owner's buffer: the totals of the owner's earlier experts
+    int base = 0;
+    for (int k = owner * epr; k < e; k++) base += s_tot[k];
+    p.dst_base[e] = base + before;
+    // the owner's own view: only its experts count below
+    const int cnt = mine ? tot : 0, used = cnt > 0;
+    const int na = (cnt + p.tn_a - 1) / p.tn_a, nb = (cnt + p.tn_b - 1) / p.tn_b;
+    int v[4] = {cnt, used, na, nb}, x[4] = {cnt, used, na, nb};
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+        for (int k = 0; k < 4; k++) { int t = __shfl_up_sync(0xffffffffu, x[k], o); if (lane >= o) x[k] += t; }
+    if (lane == 31) for (int k = 0; k < 4; k++) w_sum[wid][k] = x[k];
+    __syncthreads();
+    int off[4] = {0, 0, 0, 0};
+    for (int w = 0; w < wid; w++) for (int k = 0; k < 4; k++) off[k] += w_sum[w][k];
+    const int start = off[0] + x[0] - v[0], uidx = off[1] + x[1] - v[1], ta0 = off[2] + x[2] - v[2], tb0 = off[3] + x[3] - v[3];
+    if (used) {
+        p.ue[uidx] = e; p.ustart[uidx] = start;
+        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * p.tn_a, min(p.tn_a, cnt - t * p.tn_a), 0}; p.tiles_a[ta0 + t] = m; }
+        for (int t = 0; t < nb; t++) { MoeTile m = {uidx, start + t * p.tn_b, min(p.tn_b, cnt - t * p.tn_b), 0}; p.tiles_b[tb0 + t] = m; }
+    }
+    if (e == NEXP - 1) {
+        const int nu = uidx + used;
+        *p.nu = nu; p.ustart[nu] = start + cnt; *p.total = start + cnt; *p.ntiles_a = ta0 + na; *p.ntiles_b = tb0 + nb;
+    }
+}
+extern "C" void k_ep_plan(cudaStream_t st, const EpPlanArgs *p) { ep_plan_kernel<<<1, NEXP, 0, st>>>(*p); k_count_add(1); }
+
+// 128 threads per pair: the 2048-byte int8 row and its scale, code-sum correction and return address to the owner
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs d) {
+    const int i = blockIdx.x * 2 + (threadIdx.x >> 7), c = threadIdx.x & 127;
+    if (i >= d.np) return;
+    const int e = d.uexp[i], owner = e / d.experts_per_rank, tok = d.utok[i];
+    const int slot = d.dst_base[e] + (i - d.ustart_of_expert[e]);
+    reinterpret_cast<uint4 *>(d.peer_hq[owner] + (size_t)slot * 2048)[c] = reinterpret_cast<const uint4 *>(d.hq + (size_t)tok * 2048)[c];
+    if (c == 0) { d.peer_qs[owner][slot] = d.hqs[tok]; d.peer_qsum[owner][slot] = d.hqsum[tok]; d.peer_src[owner][slot] = make_int2(d.rank, i); }
+}
+extern "C" void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d) {
+    if (d->np <= 0) return;
+    ep_dispatch_kernel<<<(d->np + 1) / 2, 256, 0, st>>>(*d); k_count_add(1);
+}

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
     const int8_t *src = GATEUP ? a.hq : a.aq;
     for (int i = tid; i < tile.cnt * (KB / 16); i += 128) {
         int n = i / (KB / 16), q = i % (KB / 16);            // piece q covers columns 16q..16q+15
-        int row = GATEUP ? a.ptok[tile.p0 + n] : tile.p0 + n;
+        int row = (GATEUP && a.ptok) ? a.ptok[tile.p0 + n] : tile.p0 + n;
         uint4 v = *reinterpret_cast<const uint4 *>(src + (size_t)row * KB + q * 16);
         int G = q >> 3, s = (q & 7) >> 1, h = q & 1, c = G >> 1, tt = (G & 1) * 2 + h;
         *reinterpret_cast<uint4 *>(smem + ((((c * 4 + s) * TN + n) * 4 + tt) << 4)) = v;
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
             if (n >= tile.cnt) continue;
             int pair = tile.p0 + n;
             if (GATEUP) {
-                int tok = a.ptok[pair];
+                int tok = a.ptok ? a.ptok[pair] : pair;
                 int da = acc_a[j][k] - a.hqsum[tok], db = acc_b[j][k] - a.hqsum[tok];
                 float qs = a.hqs[tok];
                 float gv = __fmul_rn(__fmul_rn((float)da, qs), sca[k >> 1]), uv = __fmul_rn(__fmul_rn((float)db, qs), scb[k >> 1]);
@@ -118,8 +118,10 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
             } else {
                 int da = acc_a[j][k] - a.aqsum[pair], db = acc_b[j][k] - a.aqsum[pair];
                 float qs = a.aqs[pair];
-                a.down[(size_t)pair * 2048 + rr] = __fmul_rn(__fmul_rn((float)da, qs), sca[k >> 1]);
-                a.down[(size_t)pair * 2048 + rr + 16] = __fmul_rn(__fmul_rn((float)db, qs), scb[k >> 1]);
+                float *drow = a.down + (size_t)pair * 2048;
+                if (a.rx_src) { const int2 sp = a.rx_src[pair]; drow = a.peer_down[sp.x] + (size_t)sp.y * 2048; }   // the row goes to the token's rank
+                drow[rr] = __fmul_rn(__fmul_rn((float)da, qs), sca[k >> 1]);
+                drow[rr + 16] = __fmul_rn(__fmul_rn((float)db, qs), scb[k >> 1]);
                 if (a.dn_dots) { a.dn_dots[(size_t)pair * 2048 + rr] = da; a.dn_dots[(size_t)pair * 2048 + rr + 16] = db; }
             }
         }

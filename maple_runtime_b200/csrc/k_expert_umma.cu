@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
             __syncwarp();
             for (int n = lane; n < N; n += 32) {
-                const int pair = tile.p0 + (n < cnt ? n : 0), t = GATEUP ? a.ptok[pair] : pair;
+                const int pair = tile.p0 + (n < cnt ? n : 0), t = (GATEUP && a.ptok) ? a.ptok[pair] : pair;
                 sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
             }
             __syncwarp();
@@ -258,7 +258,9 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll
                     for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
                         const size_t pair = (size_t)(tile.p0 + c0 + j);
-                        a.down[pair * 2048 + r0] = o0[j]; a.down[pair * 2048 + r0 + 128] = o1[j];
+                        float *drow = a.down + pair * 2048;
+                        if (a.rx_src) { const int2 sp = a.rx_src[pair]; drow = a.peer_down[sp.x] + (size_t)sp.y * 2048; }   // the row goes to the token's rank
+                        drow[r0] = o0[j]; drow[r0 + 128] = o1[j];
                         if (a.dn_dots) { a.dn_dots[pair * 2048 + r0] = (int)v0[j]; a.dn_dots[pair * 2048 + r0 + 128] = (int)v1[j]; }
                     }
                 }

@@ -163,14 +163,100 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const uint16_t *__re
             if (j == 0 && b < nb) logits[(size_t)b * NEXP + e] = bias ? __fadd_rn(l, bias[e]) : l;
         }
 }
+// The prefill variant: a 32-token x 64-expert tile per CTA, each thread an 8 x 8 register tile for its lane j, the four
+// tile positions of a warp arranged 2 x 2 so that every shared-memory row a warp reads feeds two positions (0.5 bytes of
+// shared-memory traffic per FMA, half of what the bandwidth allows at the full FMA rate).  Two CTAs share an SM, one multiplies
+// while the other loads.  Same chain order per (token, expert, lane) as above.
+__global__ void __launch_bounds__(256, 2) router_logits_prefill_kernel(const uint16_t *__restrict__ W, const float *__restrict__ hn,
+                                                                      const float *__restrict__ bias, float *__restrict__ logits, int nb) {
+    constexpr int BT = 32, BE = 64, TT = 8, TE = 8;
+    extern __shared__ __align__(16) float rsm[];
+    float *hs = rsm, *ws = rsm + BT * RT_ROW;
+    const int tid = threadIdx.x, j = tid & 7, pos = tid >> 3, warp = tid >> 5, q = pos & 3;
+    const int tg = (warp & 1) * 2 + (q & 1), eg = (warp >> 1) * 2 + (q >> 1);       // 4 token groups x 8 expert groups; a warp holds 2 x 2 of them
+    const int b0 = blockIdx.y * BT, e0 = blockIdx.x * BE;
+    float acc[TT][TE];
+#pragma unroll
+    for (int a = 0; a < TT; a++)
+#pragma unroll
+        for (int c = 0; c < TE; c++) acc[a][c] = 0.0f;
+    // this thread's share of a chunk: 4 float4 of hidden rows, 2 x 8 bf16 of router rows
+    float4 ph[4]; uint4 pw[4];
+    auto fetch = [&](int c0) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int i = tid + 256 * k, r = i >> 5, c = (i & 31) * 4;
+            ph[k] = (b0 + r < nb) ? *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int i = tid + 256 * k, r = i >> 4, c = (i & 15) * 8;
+            pw[k] = *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c);
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int i = tid + 256 * k, r = i >> 5, c = (i & 31) * 4;
+            float *d = hs + r * RT_ROW + (c >> 3); const int jj = c & 7;
+            d[(jj + 0) * RT_LS] = ph[k].x; d[(jj + 1) * RT_LS] = ph[k].y; d[(jj + 2) * RT_LS] = ph[k].z; d[(jj + 3) * RT_LS] = ph[k].w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int i = tid + 256 * k, r = i >> 4, c = (i & 15) * 8;
+            float *d = ws + r * RT_ROW + (c >> 3); const uint4 v = pw[k];
+            d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
+            d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
+            d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
+            d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
+        }
+    };
+    for (int c0 = 0; c0 < HID; c0 += RT_KC) {
+        fetch(c0);                                   // the co-resident CTA of the SM covers this latency
+        __syncthreads();
+        stash();
+        __syncthreads();
+#pragma unroll
+        for (int i4 = 0; i4 < RT_KC / 8 / 4; i4++) {
+            float4 wv[TE];
+#pragma unroll
+            for (int c = 0; c < TE; c++) wv[c] = *reinterpret_cast<const float4 *>(ws + (eg * TE + c) * RT_ROW + j * RT_LS + i4 * 4);
+#pragma unroll
+            for (int a = 0; a < TT; a++) {
+                const float4 hv = *reinterpret_cast<const float4 *>(hs + (tg * TT + a) * RT_ROW + j * RT_LS + i4 * 4);
+#pragma unroll
+                for (int c = 0; c < TE; c++) {
+                    acc[a][c] = __fmaf_rn(wv[c].x, hv.x, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].y, hv.y, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].z, hv.z, acc[a][c]);
+                    acc[a][c] = __fmaf_rn(wv[c].w, hv.w, acc[a][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < TT; a++)
+#pragma unroll
+        for (int c = 0; c < TE; c++) {
+            float l = acc[a][c];
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 4));
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 1));
+            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 2));
+            const int b = b0 + tg * TT + a, e = e0 + eg * TE + c;
+            if (j == 0 && b < nb) logits[(size_t)b * NEXP + e] = bias ? __fadd_rn(l, bias[e]) : l;
+        }
+}
 extern "C" void k_router_logits(cudaStream_t st, const uint16_t *router, const float *hn, const float *bias, float *logits, int nb) {
     if (nb <= 0) return;
     if (nb <= 256) {   // few tokens: small tiles so that the grid still covers the SMs
         dim3 grid(NEXP / 8, (nb + 7) / 8);
         router_logits_kernel<1, 2, 8, 4><<<grid, 256, 0, st>>>(router, hn, bias, logits, nb);
     } else {
-        dim3 grid(NEXP / 32, (nb + 31) / 32);
-        router_logits_kernel<4, 8, 8, 4><<<grid, 256, 0, st>>>(router, hn, bias, logits, nb);
+        const size_t smem = (size_t)(32 + 64) * RT_ROW * sizeof(float);
+        static bool attr_done = false;
+        if (!attr_done) { cudaFuncSetAttribute(router_logits_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
+        dim3 grid(NEXP / 64, (nb + 31) / 32);
+        router_logits_prefill_kernel<<<grid, 256, smem, st>>>(router, hn, bias, logits, nb);
     }
     g_launches++;
 }
@@ -247,7 +333,7 @@ __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restr
     atomicOr(&mask[(size_t)e * mask_words + (b >> 5)], 1u << (b & 31));
 }
 __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__restrict__ mask, int mask_words, int *__restrict__ nu_out,
-                                                          int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart,
+                                                          int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart, int *__restrict__ ecnt,
                                                           MoeTile *__restrict__ ta, int *__restrict__ nta, int tna,
                                                           MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb) {
     __shared__ int s_cnt[NEXP], s_used[NEXP], s_ta[NEXP], s_tb[NEXP];
@@ -255,6 +341,7 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
     int cnt = 0;
     for (int w = 0; w < mask_words; w++) cnt += __popc(mask[(size_t)e * mask_words + w]);
+    if (ecnt) ecnt[e] = cnt;
     int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
     // inclusive warp scans of the four quantities
     int c = cnt, u = used, a = na, b = nb_;
@@ -283,7 +370,7 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
 }
 __global__ void __launch_bounds__(256) group_fill_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ estart,
                                                          const int *__restrict__ top, const float *__restrict__ topw,
-                                                         int *__restrict__ utok, float *__restrict__ uw, int *__restrict__ slot) {
+                                                         int *__restrict__ utok, float *__restrict__ uw, int *__restrict__ slot, int *__restrict__ uexp) {
     const int lane = threadIdx.x & 31, e = blockIdx.x * 8 + (threadIdx.x >> 5);
     int base = estart[e];
     if (base < 0) return;
@@ -298,7 +385,7 @@ __global__ void __launch_bounds__(256) group_fill_kernel(const unsigned *__restr
             int b = (w0 + lane) * 32 + bit, s = 0;
 #pragma unroll
             for (int k = 0; k < TOPK; k++) if (top[b * TOPK + k] == e) s = k;
-            utok[r] = b; uw[r] = topw[b * TOPK + s]; slot[b * TOPK + s] = r; r++;
+            utok[r] = b; uw[r] = topw[b * TOPK + s]; slot[b * TOPK + s] = r; if (uexp) uexp[r] = e; r++;
         }
         base += __shfl_sync(0xffffffffu, incl, 31);
     }
@@ -321,9 +408,9 @@ extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     const int np = g->nb * TOPK;
     cudaMemsetAsync(g->mask, 0, (size_t)NEXP * g->mask_words * sizeof(unsigned), st);
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
-    group_scan_kernel<<<1, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart,
+    group_scan_kernel<<<1, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
                                           g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b);
-    group_fill_kernel<<<NEXP / 8, 256, 0, st>>>(g->mask, g->mask_words, g->estart, g->top, g->topw, g->utok, g->uw, g->slot);
+    group_fill_kernel<<<NEXP / 8, 256, 0, st>>>(g->mask, g->mask_words, g->estart, g->top, g->topw, g->utok, g->uw, g->slot, g->uexp);
     group_tp_kernel<<<(g->nb + 127) / 128, 128, 0, st>>>(g->slot, g->tp, g->nb);
     g_launches += 4;
 }
@@ -332,7 +419,8 @@ extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
 // SiLU-output int8 (the prep call of maple.c:831 on 512 values): one warp per pair, 16 values per lane.
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) actq_kernel(const float *__restrict__ act, int8_t *__restrict__ aq, float *__restrict__ aqs,
-                                                   int *__restrict__ aqsum, int np) {
+                                                   int *__restrict__ aqsum, int np, const int *__restrict__ np_dev) {
+    if (np_dev) np = min(np, *np_dev);
     const int lane = threadIdx.x & 31, a = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (a >= np) return;
     const float4 *r = reinterpret_cast<const float4 *>(act + (size_t)a * FFN) + lane * 4;
@@ -354,9 +442,8 @@ __global__ void __launch_bounds__(256) actq_kernel(const float *__restrict__ act
     if (lane == 0) { aqs[a] = s; aqsum[a] = tot; }
 }
 extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max) {
-    (void)np_dev;
     if (np_max <= 0) return;
-    actq_kernel<<<(np_max + 7) / 8, 256, 0, st>>>(act, aq, aqs, aqsum, np_max); g_launches++;
+    actq_kernel<<<(np_max + 7) / 8, 256, 0, st>>>(act, aq, aqs, aqsum, np_max, np_dev); g_launches++;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -364,7 +451,8 @@ extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs
 // pair, 16 values per lane.  act (optional) receives the fp32 activations for stage comparisons.
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
-                                                         int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np) {
+                                                         int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np, const int *__restrict__ np_dev) {
+    if (np_dev) np = min(np, *np_dev);
     __shared__ unsigned long long tab[32];
     if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
     __syncthreads();
@@ -398,9 +486,9 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
     for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     if (lane == 0) { aqs[a] = s; aqsum[a] = tot; }
 }
-extern "C" void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np) {
+extern "C" void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np, const int *np_dev) {
     if (np <= 0) return;
-    silu_quant_kernel<<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np); g_launches++;
+    silu_quant_kernel<<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np, np_dev); g_launches++;
 }
 
 // ------------------------------------------------------------------------------------------------------------

@@ -21,7 +21,7 @@ typedef struct {
     const ExpertMaps *maps;  /* same indexing; only the tcgen05 kernels read it */
     const int *ue;
     const MoeTile *tiles; const int *ntiles; int max_tiles;
-    const int *ptok;         /* [np] token of each pair */
+    const int *ptok;         /* [np] token of each pair; NULL = the per-token arrays below are already in pair order (expert parallel) */
     /* gate+up inputs */
     const int8_t *hq; const float *hqs; const int *hqsum;          /* per token */
     float *act;              /* [np][512] */
@@ -30,6 +30,8 @@ typedef struct {
     float *down;             /* [np][2048] */
     /* optional stage outputs (NULL = off) */
     float *gate, *up; int32_t *gu_dots, *dn_dots;
+    /* expert parallel: the down rows go to the rank that owns the token: rx_src[pair] = (rank, pair slot there), peer_down[rank] = its [pairs][2048] buffer */
+    const int2 *rx_src; float *const *peer_down;
     int *err;                /* set to 1 by a kernel whose bounded wait ran out */
 } ExpertArgs;
 
@@ -43,12 +45,14 @@ typedef struct {
     unsigned *mask;          /* [256][mask_words] */
     int mask_words;
     int *nu, *ue, *estart, *ustart, *utok, *slot, *tp; float *uw;
+    int *ecnt, *uexp;        /* optional: pairs per expert [256], expert of every pair [np] (expert parallel) */
     MoeTile *tiles_a, *tiles_b; int *ntiles_a, *ntiles_b; int tn_a, tn_b;   /* two tile lists: sizes tn_a and tn_b */
 } GroupArgs;
 void k_group(cudaStream_t st, const GroupArgs *g);
+/* np_dev (optional, device): the pair count when only a capacity np_max is known on the host */
 void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max);
 /* SiLU*up then per-pair int8 from stored gate and up (the tensor-core path); act may be NULL */
-void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np);
+void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np, const int *np_dev);
 void k_combine(cudaStream_t st, const float *down, const float *uw, const int *tp, const float *init, float *out, int nb);
 
 /* register-decode + mma.sync grouped kernels (any token count; the decode-batch path); tn = 8 or 32 */
@@ -61,6 +65,23 @@ void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
 void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
+
+/* ---- expert parallel (k_ep.cu) ---- */
+typedef struct {
+    const int *all_cnt;      /* [world][256] pairs per expert of every rank */
+    int rank, world;
+    int *dst_base;           /* [256] where this rank's pairs of expert e start in the owner's receive buffer */
+    int *nu, *ue, *ustart;   /* the owner's view of its received pairs: used local experts (global ids), starts, total at ustart[nu] */
+    int *total;              /* [1] received pairs */
+    MoeTile *tiles_a, *tiles_b; int *ntiles_a, *ntiles_b; int tn_a, tn_b;
+} EpPlanArgs;
+void k_ep_plan(cudaStream_t st, const EpPlanArgs *p);
+typedef struct {
+    const int8_t *hq; const float *hqs; const int *hqsum;        /* per token, this rank */
+    const int *utok, *uexp, *ustart_of_expert, *dst_base; int np, rank, experts_per_rank;
+    int8_t *const *peer_hq; float *const *peer_qs; int *const *peer_qsum; int2 *const *peer_src;   /* [world] receive buffers */
+} EpDispatchArgs;
+void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d);
 
 void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
 

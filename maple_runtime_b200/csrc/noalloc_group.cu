@@ -64,6 +64,7 @@ extern "C" int gmoe_group_noalloc(const int *top, const float *topw, int nb, int
     g.top = top; g.topw = topw; g.nb = nb;
     g.mask = s->mask; g.mask_words = (nb + 31) / 32;
     g.nu = nu; g.ue = ue; g.estart = s->estart; g.ustart = ustart; g.utok = utok; g.slot = s->slot; g.tp = tp; g.uw = uw;
+    g.ecnt = NULL; g.uexp = NULL;
     g.tiles_a = s->tiles_a; g.tiles_b = s->tiles_b; g.ntiles_a = s->ntiles_a; g.ntiles_b = s->ntiles_b; g.tn_a = 8; g.tn_b = 128;
     k_group(static_cast<cudaStream_t>(stream), &g);   // clears the masks first (cudaMemsetAsync), then four kernels; no allocation
     e = cudaGetLastError();
