@@ -438,10 +438,10 @@ static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc,
             S.h_maps[u] = S.map_cache[hsh].m;
         }
         for (int p = ustart[u]; p < ustart[u + 1]; p += tn) {   /* gpu_pre.m:329-333 */
-            MoeTile m = {u, p, ustart[u + 1] - p < tn ? ustart[u + 1] - p : tn, 0}; S.h_tiles[nt++] = m;
+            MoeTile m = {u, p, ustart[u + 1] - p < tn ? ustart[u + 1] - p : tn, u}; S.h_tiles[nt++] = m;
         }
         for (int p = ustart[u]; p < ustart[u + 1]; p += UMMA_TN) {
-            MoeTile m = {u, p, ustart[u + 1] - p < UMMA_TN ? ustart[u + 1] - p : UMMA_TN, 0}; h_tb[ntb++] = m;
+            MoeTile m = {u, p, ustart[u + 1] - p < UMMA_TN ? ustart[u + 1] - p : UMMA_TN, u}; h_tb[ntb++] = m;
         }
     }
     for (int a = 0; a < np; a++) if (ptok[a] < 0 || ptok[a] >= nb) return fail(who, "ptok[%d] = %d", a, ptok[a]);

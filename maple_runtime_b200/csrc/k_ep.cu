@@ -42,8 +42,8 @@ __global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p) {
     const int start = off[0] + x[0] - v[0], uidx = off[1] + x[1] - v[1], ta0 = off[2] + x[2] - v[2], tb0 = off[3] + x[3] - v[3];
     if (used) {
         p.ue[uidx] = e; p.ustart[uidx] = start;
-        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * p.tn_a, min(p.tn_a, cnt - t * p.tn_a), 0}; p.tiles_a[ta0 + t] = m; }
-        for (int t = 0; t < nb; t++) { MoeTile m = {uidx, start + t * p.tn_b, min(p.tn_b, cnt - t * p.tn_b), 0}; p.tiles_b[tb0 + t] = m; }
+        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * p.tn_a, min(p.tn_a, cnt - t * p.tn_a), e}; p.tiles_a[ta0 + t] = m; }
+        for (int t = 0; t < nb; t++) { MoeTile m = {uidx, start + t * p.tn_b, min(p.tn_b, cnt - t * p.tn_b), e}; p.tiles_b[tb0 + t] = m; }
     }
     if (e == NEXP - 1) {
         const int nu = uidx + used;

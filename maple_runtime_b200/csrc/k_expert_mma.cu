@@ -44,8 +44,7 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
     const int tile_i = blockIdx.y;
     if (tile_i >= *a.ntiles) return;
     const MoeTile tile = a.tiles[tile_i];
-    const int ex = a.ue ? a.ue[tile.u] : tile.u;
-    const ExpertPtrs ep = a.tab[ex];
+    const ExpertPtrs ep = a.tab[tile.ex];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
 
     // stage the tile's activation vectors (16-byte pieces) in fragment order

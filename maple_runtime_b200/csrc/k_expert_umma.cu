@@ -50,7 +50,7 @@ struct __align__(16) UmShared {
     uint64_t b_full[UM_BSTAGES], b_empty[UM_BSTAGES], acc_full, acc_empty;
     uint32_t tmem_base; int abort_flag;
     unsigned long long exp_tab[32];
-    float m_qs[8][UM_TN]; int m_qsum[8][UM_TN];      // per epilogue warp: scale and code-sum correction of the tile's tokens
+    __align__(16) float m_qs[8][UM_TN]; __align__(16) int m_qsum[8][UM_TN];      // per epilogue warp: scale and code-sum correction of the tile's tokens
 };
 
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
@@ -70,7 +70,8 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     uint8_t *base = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *wsm = base;                                              // UM_WSTAGES x 32 KB packed weights
     uint8_t *bsm = base + UM_WSTAGES * UM_WBYTES;                      // UM_BSTAGES x 32 KB int8 activations (two 16 KB blocks per round)
-    UmShared *sh = reinterpret_cast<UmShared *>(bsm + UM_BSTAGES * UM_BBYTES);
+    __shared__ UmShared sh_static;                                    // static, so that the compiler knows these accesses are shared-memory ones
+    UmShared *sh = &sh_static;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int MB = GATEUP ? 4 : 8, NSB = KB / 4;
     const int nitems = *a.ntiles * MB;
@@ -137,10 +138,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
         // ---------------- weight TMA (one lane): per stage the 128 rows of accumulator 0 and the 128 of accumulator 1 ----------------
         if (lane == 0) {
             uint32_t wcnt = 0;
+            MoeTile tnext = blockIdx.x < nitems ? a.tiles[blockIdx.x / MB] : MoeTile{0, 0, 0, 0};      // one item ahead: no load latency at an item's start
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
-                const MoeTile tile = a.tiles[item / MB];
-                const int mb = item % MB, ex = a.ue ? a.ue[tile.u] : tile.u;
-                const ExpertMaps *em = a.maps + ex;
+                const MoeTile tile = tnext;
+                if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
+                const int mb = item % MB;
+                const ExpertMaps *em = a.maps + tile.ex;
                 for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
                     const int ws = wcnt % UM_WSTAGES;
                     if (!TWAIT(0, mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
@@ -160,8 +163,10 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
         // ---------------- B TMA (one lane): per round two boxes of 128 rows x 128 bytes of the pair-ordered int8 activations ----------------
         if (lane == 0) {
             uint32_t bcnt = 0;
+            MoeTile tnext = blockIdx.x < nitems ? a.tiles[blockIdx.x / MB] : MoeTile{0, 0, 0, 0};
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
-                const MoeTile tile = a.tiles[item / MB];
+                const MoeTile tile = tnext;
+                if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
                 for (int kb = 0; kb < KB && live; kb += 2, bcnt++) {
                     const int s = bcnt % UM_BSTAGES;
                     if (!TWAIT(0, mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
@@ -180,8 +185,10 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             const uint32_t afull0 = smem_u32(&sh->a_full[h][0]), aempty0 = smem_u32(&sh->a_empty[h][0]);
             const uint32_t bfull0 = smem_u32(&sh->b_full[0]), bempty0 = smem_u32(&sh->b_empty[0]);
             uint32_t as = 0, ap = 0, bs = 0, bp = 0, icnt = 0;
+            MoeTile tnext = blockIdx.x < nitems ? a.tiles[blockIdx.x / MB] : MoeTile{0, 0, 0, 0};
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
-                const MoeTile tile = a.tiles[item / MB];
+                const MoeTile tile = tnext;
+                if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
                 const uint32_t idesc = idesc_i8_u8s8((uint32_t)((tile.cnt + 15) & ~15));
                 if (!TWAIT(0, mbar_wait(&sh->acc_empty, (icnt & 1) ^ 1, abortp))) { live = false; break; }
                 tc_fence_after();
@@ -213,10 +220,20 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
         // ---------------- epilogue: lane = weight row, columns = tokens; warps 12-15 take the even 16-column pieces, 16-19 the odd ----------------
         const int ew = warp - 12, q4 = warp & 3, half = ew >> 2, row = q4 * 32 + lane;   // a warp reaches the tensor-memory lanes 32 (warp % 4) ..
         uint32_t icnt = 0;
-        for (int item = blockIdx.x; item < nitems && live; item += gridDim.x, icnt++) {
-            const MoeTile tile = a.tiles[item / MB];
-            const int mb = item % MB, ex = a.ue ? a.ue[tile.u] : tile.u, cnt = tile.cnt, N = (cnt + 15) & ~15;
-            const ExpertPtrs ep = a.tab[ex];
+        // the item header is a chain tile -> pointer table -> scales: the tile is read two items ahead and the pointer table one item
+        // ahead, so that an item starts with everything but the scale values in registers
+        const int stride = gridDim.x;
+        MoeTile t1 = blockIdx.x < nitems ? a.tiles[blockIdx.x / MB] : MoeTile{0, 0, 0, 0};
+        MoeTile t2 = (int)blockIdx.x + stride < nitems ? a.tiles[(blockIdx.x + stride) / MB] : MoeTile{0, 0, 0, 0};
+        ExpertPtrs ep1 = a.tab[t1.ex];
+        for (int item = blockIdx.x; item < nitems && live; item += stride, icnt++) {
+            const MoeTile tile = t1; const ExpertPtrs ep = ep1;
+            t1 = t2; ep1 = a.tab[t1.ex];
+            if (item + 2 * stride < nitems) t2 = a.tiles[(item + 2 * stride) / MB];
+            const int mb = item % MB, cnt = tile.cnt, N = (cnt + 15) & ~15;
+#ifdef UMMA_TRACE
+            long long tq0 = clock64();
+#endif
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
             const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
             __syncwarp();
@@ -225,6 +242,9 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
             }
             __syncwarp();
+#ifdef UMMA_TRACE
+            wacc[1] += clock64() - tq0;
+#endif
             if (!TWAIT(0, mbar_wait(&sh->acc_full, icnt & 1, abortp))) { live = false; break; }
             tc_fence_after();
             const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16);
@@ -232,38 +252,68 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             if (half * 16 >= N) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->acc_empty); }
             for (int c0 = half * 16; c0 < N; c0 += 32) {
                 uint32_t v0[16], v1[16];
+#ifdef UMMA_TRACE
+                long long tq1 = clock64();
+#endif
                 tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 128 + c0, v1);
                 tmem_ld_wait();
+#ifdef UMMA_TRACE
+                wacc[2] += clock64() - tq1; tq1 = clock64();
+#endif
                 if (c0 == c_last * 16) {   // the buffer is in registers: hand it back before the arithmetic
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->acc_empty);
                 }
                 float o0[16], o1[16];
+                {   // scale and code-sum correction of the piece's 16 tokens: eight 128-bit shared-memory reads
+                    const int4 *qsv = reinterpret_cast<const int4 *>(&sh->m_qsum[ew][c0]);
+                    const float4 *qfv = reinterpret_cast<const float4 *>(&sh->m_qs[ew][c0]);
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int qsum = sh->m_qsum[ew][c0 + j]; const float qs = sh->m_qs[ew][c0 + j];
-                    const int d0 = (int)v0[j] - qsum, d1 = (int)v1[j] - qsum;
-                    o0[j] = __fmul_rn(__fmul_rn((float)d0, qs), s0); o1[j] = __fmul_rn(__fmul_rn((float)d1, qs), s1);
-                    v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
+                    for (int g4 = 0; g4 < 4; g4++) {
+                        const int4 qs4 = qsv[g4]; const float4 qf4 = qfv[g4];
+                        const int qsum[4] = {qs4.x, qs4.y, qs4.z, qs4.w}; const float qs[4] = {qf4.x, qf4.y, qf4.z, qf4.w};
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const int j = g4 * 4 + k, d0 = (int)v0[j] - qsum[k], d1 = (int)v1[j] - qsum[k];
+                            o0[j] = __fmul_rn(__fmul_rn((float)d0, qs[k]), s0); o1[j] = __fmul_rn(__fmul_rn((float)d1, qs[k]), s1);
+                            v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
+                        }
+                    }
                 }
+                const int lim = cnt - c0;                                 // tokens of this piece that exist
                 if (GATEUP) {
+                    // one base pointer per thread; the token index only adds a constant, so a store is one instruction
+                    float *gp = a.gate + (size_t)(tile.p0 + c0) * 512 + r0, *up_ = a.up + (size_t)(tile.p0 + c0) * 512 + r0;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
-                        const size_t pair = (size_t)(tile.p0 + c0 + j);
-                        a.gate[pair * 512 + r0] = o0[j]; a.up[pair * 512 + r0] = o1[j];
-                        if (a.gu_dots) { a.gu_dots[pair * 1024 + r0] = (int)v0[j]; a.gu_dots[pair * 1024 + 512 + r0] = (int)v1[j]; }
+                    for (int j = 0; j < 16; j++) if (j < lim) { gp[j * 512] = o0[j]; up_[j * 512] = o1[j]; }
+                    if (a.gu_dots) {
+                        int *dp = a.gu_dots + (size_t)(tile.p0 + c0) * 1024 + r0;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (j < lim) { dp[j * 1024] = (int)v0[j]; dp[j * 1024 + 512] = (int)v1[j]; }
+                    }
+                } else if (!a.rx_src) {
+                    float *dp = a.down + (size_t)(tile.p0 + c0) * 2048 + r0;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) if (j < lim) { dp[j * 2048] = o0[j]; dp[j * 2048 + 128] = o1[j]; }
+                    if (a.dn_dots) {
+                        int *ip = a.dn_dots + (size_t)(tile.p0 + c0) * 2048 + r0;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (j < lim) { ip[j * 2048] = (int)v0[j]; ip[j * 2048 + 128] = (int)v1[j]; }
                     }
                 } else {
+                    // expert parallel: each row goes to the rank that owns the token
 #pragma unroll
-                    for (int j = 0; j < 16; j++) if (c0 + j < cnt) {
-                        const size_t pair = (size_t)(tile.p0 + c0 + j);
-                        float *drow = a.down + pair * 2048;
-                        if (a.rx_src) { const int2 sp = a.rx_src[pair]; drow = a.peer_down[sp.x] + (size_t)sp.y * 2048; }   // the row goes to the token's rank
-                        drow[r0] = o0[j]; drow[r0 + 128] = o1[j];
-                        if (a.dn_dots) { a.dn_dots[pair * 2048 + r0] = (int)v0[j]; a.dn_dots[pair * 2048 + r0 + 128] = (int)v1[j]; }
+                    for (int j = 0; j < 16; j++) if (j < lim) {
+                        const int2 sp = a.rx_src[tile.p0 + c0 + j];
+                        float *drow = a.peer_down[sp.x] + (size_t)sp.y * 2048 + r0;
+                        drow[0] = o0[j]; drow[128] = o1[j];
+                        if (a.dn_dots) { a.dn_dots[(size_t)(tile.p0 + c0 + j) * 2048 + r0] = (int)v0[j]; a.dn_dots[(size_t)(tile.p0 + c0 + j) * 2048 + r0 + 128] = (int)v1[j]; }
                     }
                 }
+#ifdef UMMA_TRACE
+                wacc[3] += clock64() - tq1;
+#endif
             }
         }
     }
@@ -282,7 +332,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 
 template <int KB, bool GATEUP>
 static void launch(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) {
-    const size_t smem = (size_t)UM_WSTAGES * UM_WBYTES + UM_BSTAGES * UM_BBYTES + sizeof(UmShared) + 1024;
+    const size_t smem = (size_t)UM_WSTAGES * UM_WBYTES + UM_BSTAGES * UM_BBYTES + 1024;
     static int sms = 0;
     if (!sms) {
         int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -360,8 +360,8 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
     estart[e] = used ? start : -1;
     if (used) {
         ue[uidx] = e; ustart[uidx] = start;
-        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * tna, min(tna, cnt - t * tna), 0}; ta[s_ta[e] + t] = m; }
-        for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * tnb, min(tnb, cnt - t * tnb), 0}; tb[s_tb[e] + t] = m; }
+        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * tna, min(tna, cnt - t * tna), e}; ta[s_ta[e] + t] = m; }
+        for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * tnb, min(tnb, cnt - t * tnb), e}; tb[s_tb[e] + t] = m; }
     }
     if (e == NEXP - 1) {
         int nu = uidx + used;

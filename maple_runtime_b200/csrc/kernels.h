@@ -14,7 +14,7 @@ typedef struct { const uint8_t *gc, *uc, *dc; const float *gs, *us, *ds; } Exper
 typedef struct __attribute__((aligned(64))) { unsigned char b[128]; } TMap;
 typedef struct { TMap gate, up, down; } ExpertMaps;
 /* one unit of grouped-GEMM work: used expert u, first pair p0, cnt pairs (gpu_pre.m:329-333 uses the same triple) */
-typedef struct { int u, p0, cnt, pad; } MoeTile;
+typedef struct { int u, p0, cnt, ex; } MoeTile;   /* ex: index of the expert in ExpertArgs.tab / .maps */
 
 typedef struct {
     const ExpertPtrs *tab;   /* indexed by ue[u] when ue != NULL, else by u */

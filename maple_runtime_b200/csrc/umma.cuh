@@ -14,39 +14,29 @@ __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+// One poll.  The suspend-time hint lets the hardware park the thread until the phase completes (or the hint runs out) instead of
+// returning at once: a waiting warp then does not take issue slots from the warps that are working.
+#define MBAR_HINT_NS 20000u
+__device__ __forceinline__ bool mbar_try_addr(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(MBAR_HINT_NS) : "memory");
     return ok != 0;
 }
-// Every wait is bounded: after MBAR_SPINS failed polls the waiter gives up, raises *abort (shared memory, seen by all
-// roles of the CTA) and returns false; callers then leave their loops, free tensor memory and return.
-#define MBAR_SPINS (1u << 22)
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort) {
-    for (uint32_t i = 0; i < MBAR_SPINS; i++) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort) return false;
-        if (i > 1024) __nanosleep(64);
-    }
-    *abort = 1;
-    return false;
-}
-
-// the same on a shared-memory address held in a register; the first poll is inline so that a completed phase costs one instruction
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) { return mbar_try_addr(smem_u32(bar), parity); }
+// Every wait is bounded: after MBAR_SPINS failed polls (each parks for up to MBAR_HINT_NS) the waiter gives up, raises *abort
+// (shared memory, seen by all roles of the CTA) and returns false; callers then leave their loops, free tensor memory and return.
+#define MBAR_SPINS (1u << 16)
 __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, volatile int *abort) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
+    if (mbar_try_addr(bar, parity)) return true;
     for (uint32_t i = 0; i < MBAR_SPINS; i++) {
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
+        if (mbar_try_addr(bar, parity)) return true;
         if (*abort) return false;
-        if (i > 1024) __nanosleep(64);
     }
     *abort = 1;
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort) { return mbar_wait_addr(smem_u32(bar), parity, abort); }
 
 // ---- tensor memory ---------------------------------------------------------------------------------------------
 // one warp, all lanes: allocates ncols (power of two >= 32) columns, the address lands in *dst (shared memory)
