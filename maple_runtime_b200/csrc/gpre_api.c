@@ -14,6 +14,8 @@
 #include "kernels.h"
 #include "synth.h"
 
+void k_count_add(long n);
+
 #define HID 2048
 #define NEXP 256
 #define TOPK 8
@@ -107,7 +109,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(hq, T * HID); ALLOC(hqs, T * 4); ALLOC(hqsum, T * 4);
     ALLOC(logits, T * NEXP * 4); ALLOC(top, P * 4); ALLOC(topw, P * 4); ALLOC(bias, NEXP * 4);
     ALLOC(ecnt, NEXP * 4); ALLOC(uexp, P * 4);
-    ALLOC(mask, (size_t)NEXP * S.mask_words * 4); ALLOC(nu, 16); ALLOC(ue, NEXP * 4); ALLOC(estart, NEXP * 4);
+    ALLOC(mask, ((size_t)NEXP * S.mask_words + NEXP) * 4); ALLOC(nu, 16); ALLOC(ue, NEXP * 4); ALLOC(estart, NEXP * 4);
     ALLOC(ustart, (NEXP + 1) * 4); ALLOC(utok, P * 4); ALLOC(uw, P * 4); ALLOC(slot, P * 4); ALLOC(tp, P * 4);
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);
@@ -241,6 +243,12 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
 
 /* ---- per-stage events ------------------------------------------------------------------------------------------ */
 static long g_before;
+/* inside a stream capture the event becomes an event-record node of the graph, re-recorded at every replay */
+static void prof_record(cudaEvent_t ev) {
+    enum cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(S.st, &cs);
+    if (cs == cudaStreamCaptureStatusActive) cudaEventRecordWithFlags(ev, S.st, cudaEventRecordExternal); else cudaEventRecord(ev, S.st);
+}
 static void prof_begin(int stage) {
     if (!(S.prof_mask >> stage & 1u)) return;
     if (S.pev_n + 2 > S.pev_cap) {
@@ -252,11 +260,11 @@ static void prof_begin(int stage) {
         S.pev = ev; S.pev_stage = st; S.pev_launch = ln; S.pev_cap = cap;
     }
     g_before = k_count();
-    cudaEventRecord(S.pev[S.pev_n], S.st);
+    prof_record(S.pev[S.pev_n]);
 }
 static void prof_end(int stage) {
     if (!(S.prof_mask >> stage & 1u) || S.pev_n + 2 > S.pev_cap) return;
-    cudaEventRecord(S.pev[S.pev_n + 1], S.st);
+    prof_record(S.pev[S.pev_n + 1]);
     S.pev_stage[S.pev_n] = (unsigned char)stage; S.pev_launch[S.pev_n] = k_count() - g_before; S.pev_n += 2;
 }
 int gmoe_profile(unsigned mask) { if (!S.ready) return fail("gmoe", "not initialised"); S.prof_mask = mask; return 0; }
@@ -346,6 +354,44 @@ static double finish(const char *who) {
     return ms * 1e-3;
 }
 
+/* ---- the layer loop as a CUDA graph: one launch per call instead of a dozen per layer -------------------------------------
+ * Every kernel takes its sizes from device memory, so the sequence for (nb, l0, nl, bias?, path) is the same every time and can
+ * be replayed.  The second call with a key captures it (the first runs plainly, so that one-time set-up calls made by the
+ * launchers happen outside a capture).  Per-stage events are captured as event-record nodes, so gmoe_profile_read then reports the
+ * last replay.  Not used while stages are kept, under expert parallelism, or when GMOE_GRAPH=0 is set. */
+#define NGRAPH 16
+static struct { int nb, l0, nl, bias, path, prof, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
+static int graphs_on(void) {
+    static int on = -1;
+    if (on < 0) { const char *e = getenv("GMOE_GRAPH"); on = !(e && e[0] == '0'); }
+    return on && !S.keep && !S.ep_on;
+}
+static int layers_enqueue(int nb, int l0, int nl, const float *bd) {
+    if (!graphs_on()) { for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd); return 0; }
+    int k = -1, free_k = -1;
+    for (int i = 0; i < NGRAPH; i++) {
+        if (GR[i].seen && GR[i].nb == nb && GR[i].l0 == l0 && GR[i].nl == nl && GR[i].bias == (bd != NULL) && GR[i].path == S.path && GR[i].prof == (int)S.prof_mask) { k = i; break; }
+        if (!GR[i].seen && free_k < 0) free_k = i;
+    }
+    if (k < 0) {   /* first sight: run plainly and remember the key */
+        for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+        if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path; GR[free_k].prof = (int)S.prof_mask; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
+        return 0;
+    }
+    if (!GR[k].exec) {
+        cudaGraph_t g = NULL; long before = k_count();
+        if (cudaStreamBeginCapture(S.st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd); return 0; }
+        for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+        cudaError_t e = cudaStreamEndCapture(S.st, &g);
+        GR[k].launches = k_count() - before;
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&GR[k].exec, g, 0);
+        if (g) cudaGraphDestroy(g);
+        if (e != cudaSuccess) { GR[k].exec = NULL; GR[k].seen = 2; cudaGetLastError(); return fail("gmoe", "graph capture of the layer loop: %s", cudaGetErrorString(e)); }
+    } else k_count_add(GR[k].launches);
+    CU("gmoe", cudaGraphLaunch(GR[k].exec, S.st));
+    return 0;
+}
+
 double gmoe_moe(int L, const float *x, int nb, float *y, const float *bias) {
     if (check_call("gmoe", L, nb)) return -1.0;
     CUD("gmoe", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
@@ -361,7 +407,7 @@ int gmoe_forward_dev(int nb, int l0, int nl, const float *bias) {
     for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1;
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
-    for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+    if (layers_enqueue(nb, l0, nl, bd)) return -1;
     cudaEventRecord(S.e1, S.st);
     S.nb_cur = nb;
     return 0;
@@ -380,7 +426,7 @@ int gmoe_forward_chunk(int chunk, int nb, int l0, int nl, const float *bias) {
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     cudaMemcpyAsync(S.x, S.ring + (size_t)chunk * nb * HID, (size_t)nb * HID * 4, cudaMemcpyDeviceToDevice, S.st);
-    for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+    if (layers_enqueue(nb, l0, nl, bd)) return -1;
     cudaEventRecord(S.e1, S.st);
     S.nb_cur = nb; return 0;
 }
@@ -399,7 +445,7 @@ double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias) {   /* 
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
-    for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+    if (layers_enqueue(nb, l0, nl, bd)) return -1.0;
     CUD("gmoe", cudaMemcpyAsync(x, S.x, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
     cudaEventRecord(S.e1, S.st);
     S.nb_cur = nb;

@@ -331,6 +331,7 @@ __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restr
     if (i >= np) return;
     int b = i >> 3, e = top[i];
     atomicOr(&mask[(size_t)e * mask_words + (b >> 5)], 1u << (b & 31));
+    atomicAdd(&mask[(size_t)NEXP * mask_words + e], 1u);        // pairs per expert, kept behind the bit rows (integer adds: any order, same sum)
 }
 __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__restrict__ mask, int mask_words, int *__restrict__ nu_out,
                                                           int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart, int *__restrict__ ecnt,
@@ -339,8 +340,7 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
     __shared__ int s_cnt[NEXP], s_used[NEXP], s_ta[NEXP], s_tb[NEXP];
     __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
-    int cnt = 0;
-    for (int w = 0; w < mask_words; w++) cnt += __popc(mask[(size_t)e * mask_words + w]);
+    const int cnt = (int)mask[(size_t)NEXP * mask_words + e];
     if (ecnt) ecnt[e] = cnt;
     int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
     // inclusive warp scans of the four quantities
@@ -406,7 +406,7 @@ __global__ void group_tp_kernel(const int *__restrict__ slot, int *__restrict__ 
 extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
     const int np = g->nb * TOPK;
-    cudaMemsetAsync(g->mask, 0, (size_t)NEXP * g->mask_words * sizeof(unsigned), st);
+    cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit rows + the 256 counters behind them
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
     group_scan_kernel<<<1, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
                                           g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b);

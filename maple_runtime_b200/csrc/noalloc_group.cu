@@ -22,7 +22,7 @@
 #define NA_TILES (NA_MAXTOK * 8 / 8 + 256)
 
 struct NaScratch {
-    unsigned mask[256 * NA_WORDS];      // bit b of row e: token b chose expert e (must be zero at the start of a call)
+    unsigned mask[256 * NA_WORDS + 256]; // bit b of row e: token b chose expert e, then one counter per expert (must be zero at the start of a call)
     int estart[256];
     int slot[NA_MAXTOK * 8];
     MoeTile tiles_a[NA_TILES], tiles_b[NA_TILES];
