@@ -52,6 +52,9 @@ int gmoe_forward_dev(int nb, int l0, int nl, const float *bias);
  * asynchronously like gmoe_forward_dev. */
 int gmoe_chunks_upload(const float *x, int nb, int nchunks);
 int gmoe_forward_chunk(int chunk, int nb, int l0, int nl, const float *bias);
+/* The layer loop of gmoe_forward* is replayed as a CUDA graph from the second call with the same (nb, l0, nl) on (one launch per
+ * call).  on = 0 switches that off (also: environment GMOE_GRAPH=0), e.g. to time every stage with gmoe_profile. */
+int gmoe_set_graph(int on);
 /* Waits for the stream; returns the GPU seconds between the last gmoe_forward_dev's first and last kernel. */
 double gmoe_sync(void);
 /* rmsnorm(post_ln[L]) of the device-resident hidden state + int8 + router logits: the part of gfull_attn

@@ -310,7 +310,9 @@ static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int
         if (um) k_gateup_umma(S.st, &a, &S.bmap_hq); else k_gateup_mma(S.st, &a, tn);
         prof_end(4);
     }
-    if (which & 2) {
+    const int fuse_q = !um && tn == 8 && which == 7;           /* decode batches: the down kernel quantises the SiLU outputs itself */
+    if (fuse_q) { a.act_for_down = S.act; a.aq_out = S.aq; a.aqs_out = S.aqs; a.aqsum_out = S.aqsum; }
+    if ((which & 2) && !fuse_q) {
         prof_begin(5);
         if (um) k_silu_quant(S.st, S.gate, S.up, S.keep ? S.act : NULL, S.aq, S.aqs, S.aqsum, nb * TOPK, NULL);
         else k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK);
@@ -361,11 +363,12 @@ static double finish(const char *who) {
  * last replay.  Not used while stages are kept, under expert parallelism, or when GMOE_GRAPH=0 is set. */
 #define NGRAPH 16
 static struct { int nb, l0, nl, bias, path, prof, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
+static int g_graph_on = -1;
 static int graphs_on(void) {
-    static int on = -1;
-    if (on < 0) { const char *e = getenv("GMOE_GRAPH"); on = !(e && e[0] == '0'); }
-    return on && !S.keep && !S.ep_on;
+    if (g_graph_on < 0) { const char *e = getenv("GMOE_GRAPH"); g_graph_on = !(e && e[0] == '0'); }
+    return g_graph_on && !S.keep && !S.ep_on;
 }
+int gmoe_set_graph(int on) { g_graph_on = on != 0; return 0; }
 static int layers_enqueue(int nb, int l0, int nl, const float *bd) {
     if (!graphs_on()) { for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd); return 0; }
     int k = -1, free_k = -1;

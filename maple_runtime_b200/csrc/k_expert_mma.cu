@@ -47,34 +47,73 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
     const ExpertPtrs ep = a.tab[tile.ex];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
 
-    // stage the tile's activation vectors (16-byte pieces) in fragment order
-    const int8_t *src = GATEUP ? a.hq : a.aq;
-    for (int i = tid; i < tile.cnt * (KB / 16); i += 128) {
-        int n = i / (KB / 16), q = i % (KB / 16);            // piece q covers columns 16q..16q+15
-        int row = (GATEUP && a.ptok) ? a.ptok[tile.p0 + n] : tile.p0 + n;
-        uint4 v = *reinterpret_cast<const uint4 *>(src + (size_t)row * KB + q * 16);
-        int G = q >> 3, s = (q & 7) >> 1, h = q & 1, c = G >> 1, tt = (G & 1) * 2 + h;
-        *reinterpret_cast<uint4 *>(smem + ((((c * 4 + s) * TN + n) * 4 + tt) << 4)) = v;
-    }
-    __syncthreads();
-
     const int rows_per_cta = GATEUP ? 64 : 128;
     const int r0 = blockIdx.x * rows_per_cta + warp * (GATEUP ? 16 : 32);
     const uint8_t *wa = (GATEUP ? ep.gc : ep.dc) + (size_t)(r0 + g) * (KB / 4) + t * 16;
     const uint8_t *wb = GATEUP ? ep.uc + (size_t)(r0 + g) * (KB / 4) + t * 16 : wa + 16 * (KB / 4);
+    // the weight stream starts before anything else: the first two chunks are on their way while the activations are staged
+    uint4 wq[2][4];
+#pragma unroll
+    for (int p = 0; p < 2; p++) if (p < KCH) {
+        wq[p][0] = ldg_stream(wa + p * 64); wq[p][1] = ldg_stream(wa + 8 * (KB / 4) + p * 64);
+        wq[p][2] = ldg_stream(wb + p * 64); wq[p][3] = ldg_stream(wb + 8 * (KB / 4) + p * 64);
+    }
+
+    // stage the tile's activation vectors (16-byte pieces) in fragment order
+    if (GATEUP || !a.act_for_down) {
+        const int8_t *src = GATEUP ? a.hq : a.aq;
+        for (int i = tid; i < tile.cnt * (KB / 16); i += 128) {
+            int n = i / (KB / 16), q = i % (KB / 16);            // piece q covers columns 16q..16q+15
+            int row = (GATEUP && a.ptok) ? a.ptok[tile.p0 + n] : tile.p0 + n;
+            uint4 v = *reinterpret_cast<const uint4 *>(src + (size_t)row * KB + q * 16);
+            int G = q >> 3, s = (q & 7) >> 1, h = q & 1, c = G >> 1, tt = (G & 1) * 2 + h;
+            *reinterpret_cast<uint4 *>(smem + ((((c * 4 + s) * TN + n) * 4 + tt) << 4)) = v;
+        }
+    } else {
+        // down, decode path: the SiLU outputs arrive as fp32 and are quantised here (the prep of maple.c:831), one warp per pair;
+        // every row-block CTA of the tile repeats this for the tile's few pairs, the first one also stores the result
+        float *s_qs = reinterpret_cast<float *>(smem + KCH * 4 * TN * 64); int *s_qsum = reinterpret_cast<int *>(s_qs + TN);
+        for (int n = warp; n < tile.cnt; n += 4) {
+            const int pair = tile.p0 + n;
+            const float4 *r = reinterpret_cast<const float4 *>(a.act_for_down + (size_t)pair * 512) + lane * 4;
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { float4 x = r[i]; v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w; }
+            float mx = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float sc = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, sc);
+            int tot = 0; uint32_t pk[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 16; i++) { int qi = __float2int_rn(__fmul_rn(v[i], inv)); tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3)); }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+            // lane holds columns 16 lane .. 16 lane + 15 = piece q = lane
+            const int q = lane, G = q >> 3, s = (q & 7) >> 1, h = q & 1, c = G >> 1, tt = (G & 1) * 2 + h;
+            *reinterpret_cast<uint4 *>(smem + ((((c * 4 + s) * TN + n) * 4 + tt) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (lane == 0) { s_qs[n] = sc; s_qsum[n] = tot; }
+            if (blockIdx.x == 0) {
+                reinterpret_cast<uint4 *>(a.aq_out + (size_t)pair * 512)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (lane == 0) { a.aqs_out[pair] = sc; a.aqsum_out[pair] = tot; }
+            }
+        }
+    }
+    __syncthreads();
+
     int acc_a[NBLK][4], acc_b[NBLK][4];
 #pragma unroll
     for (int j = 0; j < NBLK; j++)
 #pragma unroll
         for (int k = 0; k < 4; k++) { acc_a[j][k] = 0; acc_b[j][k] = 0; }
 
-    uint4 wa0 = ldg_stream(wa), wa1 = ldg_stream(wa + 8 * (KB / 4)), wb0 = ldg_stream(wb), wb1 = ldg_stream(wb + 8 * (KB / 4));
-#pragma unroll 1
+#pragma unroll
     for (int c = 0; c < KCH; c++) {
-        uint4 na0 = wa0, na1 = wa1, nb0 = wb0, nb1 = wb1;
-        if (c + 1 < KCH) {   // next chunk in flight while this one is multiplied
-            na0 = ldg_stream(wa + (c + 1) * 64); na1 = ldg_stream(wa + 8 * (KB / 4) + (c + 1) * 64);
-            nb0 = ldg_stream(wb + (c + 1) * 64); nb1 = ldg_stream(wb + 8 * (KB / 4) + (c + 1) * 64);
+        const uint4 wa0 = wq[c & 1][0], wa1 = wq[c & 1][1], wb0 = wq[c & 1][2], wb1 = wq[c & 1][3];
+        if (c + 2 < KCH) {   // two chunks in flight while this one is multiplied
+            wq[c & 1][0] = ldg_stream(wa + (c + 2) * 64); wq[c & 1][1] = ldg_stream(wa + 8 * (KB / 4) + (c + 2) * 64);
+            wq[c & 1][2] = ldg_stream(wb + (c + 2) * 64); wq[c & 1][3] = ldg_stream(wb + 8 * (KB / 4) + (c + 2) * 64);
         }
 #pragma unroll
         for (int s = 0; s < 4; s++) {
@@ -93,7 +132,6 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
                 mma_u8s8(acc_b[j], bz0, bz1, bw0, bw1, q.z, q.w);
             }
         }
-        wa0 = na0; wa1 = na1; wb0 = nb0; wb1 = nb1;
     }
 
     // epilogue: acc[j][0..3] = (row g, token 2t), (row g, token 2t+1), (row g+8, token 2t), (row g+8, token 2t+1)
@@ -115,8 +153,10 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
                 if (a.gate) { a.gate[(size_t)pair * 512 + rr] = gv; a.up[(size_t)pair * 512 + rr] = uv; }
                 if (a.gu_dots) { a.gu_dots[(size_t)pair * 1024 + rr] = da; a.gu_dots[(size_t)pair * 1024 + 512 + rr] = db; }
             } else {
-                int da = acc_a[j][k] - a.aqsum[pair], db = acc_b[j][k] - a.aqsum[pair];
-                float qs = a.aqs[pair];
+                int qsum_p; float qs;
+                if (a.act_for_down) { const float *s_qs = reinterpret_cast<const float *>(smem + KCH * 4 * TN * 64); qs = s_qs[n]; qsum_p = reinterpret_cast<const int *>(s_qs + TN)[n]; }
+                else { qs = a.aqs[pair]; qsum_p = a.aqsum[pair]; }
+                int da = acc_a[j][k] - qsum_p, db = acc_b[j][k] - qsum_p;
                 float *drow = a.down + (size_t)pair * 2048;
                 if (a.rx_src) { const int2 sp = a.rx_src[pair]; drow = a.peer_down[sp.x] + (size_t)sp.y * 2048; }   // the row goes to the token's rank
                 drow[rr] = __fmul_rn(__fmul_rn((float)da, qs), sca[k >> 1]);
@@ -128,7 +168,7 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
 
 template <int KCH, int NBLK, bool GATEUP>
 static void launch(cudaStream_t st, const ExpertArgs *a) {
-    const size_t smem = (size_t)KCH * 4 * NBLK * 8 * 64;
+    const size_t smem = (size_t)KCH * 4 * NBLK * 8 * 64 + (GATEUP ? 0 : NBLK * 8 * 8);   // + scale and code sum per pair when down quantises itself
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(expert_mma_kernel<KCH, NBLK, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
     dim3 grid(GATEUP ? 8 : 16, a->max_tiles);

@@ -28,6 +28,9 @@ typedef struct {
     /* down inputs */
     const int8_t *aq; const float *aqs; const int *aqsum;          /* per pair */
     float *down;             /* [np][2048] */
+    /* decode path: the down kernel quantises the fp32 SiLU outputs itself (no separate pass): act_for_down [np][512] in, and the
+     * int8 rows, scales and sums it computed are also stored here for later inspection */
+    const float *act_for_down; int8_t *aq_out; float *aqs_out; int *aqsum_out;
     /* optional stage outputs (NULL = off) */
     float *gate, *up; int32_t *gu_dots, *dn_dots;
     /* expert parallel: the down rows go to the rank that owns the token: rx_src[pair] = (rank, pair slot there), peer_down[rank] = its [pairs][2048] buffer */
