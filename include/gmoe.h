@@ -99,7 +99,7 @@ int gmoe_region_count(void);
  * allocate device memory when they need the grouping: a server working inside a memory budget fixed at start-up, a
  * plug-in inside another runtime's pool, a latency path where cudaMalloc's device-wide synchronisation is not
  * acceptable.  Same result as the grouping stage of gmoe_moe (NU, UE, USTART, UTOK, UW, tp of maple.c:924-938,
- * 1018-1019), computed with scratch that is a fixed array inside the loaded library (about 205 KB per GPU, held until
+ * 1018-1019), computed with scratch that is a fixed array inside the loaded library (about 270 KB per GPU, held until
  * the process exits) instead of buffers from cudaMalloc.  All pointers are DEVICE pointers owned by the caller:
  *   top [nb][8] expert ids, topw [nb][8] routing weights  ->  nu [1], ue [256], ustart [257], utok [nb*8], uw [nb*8],
  *   tp [nb*8].  stream: a cudaStream_t (NULL = the default stream); the work is queued there, not waited for.

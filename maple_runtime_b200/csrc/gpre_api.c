@@ -109,7 +109,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(hq, T * HID); ALLOC(hqs, T * 4); ALLOC(hqsum, T * 4);
     ALLOC(logits, T * NEXP * 4); ALLOC(top, P * 4); ALLOC(topw, P * 4); ALLOC(bias, NEXP * 4);
     ALLOC(ecnt, NEXP * 4); ALLOC(uexp, P * 4);
-    ALLOC(mask, ((size_t)NEXP * S.mask_words + NEXP) * 4); ALLOC(nu, 16); ALLOC(ue, NEXP * 4); ALLOC(estart, NEXP * 4);
+    ALLOC(mask, ((size_t)2 * NEXP * S.mask_words + NEXP) * 4); ALLOC(nu, 16); ALLOC(ue, NEXP * 4); ALLOC(estart, NEXP * 4);
     ALLOC(ustart, (NEXP + 1) * 4); ALLOC(utok, P * 4); ALLOC(uw, P * 4); ALLOC(slot, P * 4); ALLOC(tp, P * 4);
     ALLOC(tiles_a, (P / 8 + NEXP) * sizeof(MoeTile)); ALLOC(tiles_b, (P / 8 + NEXP) * sizeof(MoeTile));
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);

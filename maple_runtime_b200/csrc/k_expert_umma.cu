@@ -346,13 +346,19 @@ extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bm
 
 // ---- rows of the per-token int8 matrix copied into pair (expert-grouped) order: the B operand the TMA can tile ----
 __global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restrict__ src, const int *__restrict__ rows, int8_t *__restrict__ dst, int np) {
-    const int pair = blockIdx.x * 2 + (threadIdx.x >> 7), c = threadIdx.x & 127;
-    if (pair >= np) return;
-    reinterpret_cast<uint4 *>(dst + (size_t)pair * 2048)[c] = reinterpret_cast<const uint4 *>(src + (size_t)rows[pair] * 2048)[c];
+    // 8 pairs per CTA: each thread moves one 16-byte piece of four rows, all four loads in flight together
+    const int p0 = blockIdx.x * 8 + (threadIdx.x >> 7) * 4, c = threadIdx.x & 127;
+    int r[4]; uint4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) r[k] = p0 + k < np ? rows[p0 + k] : 0;
+#pragma unroll
+    for (int k = 0; k < 4; k++) v[k] = reinterpret_cast<const uint4 *>(src + (size_t)r[k] * 2048)[c];
+#pragma unroll
+    for (int k = 0; k < 4; k++) if (p0 + k < np) reinterpret_cast<uint4 *>(dst + (size_t)(p0 + k) * 2048)[c] = v[k];
 }
 extern "C" void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np) {
     if (np <= 0) return;
-    gather_rows_kernel<<<(np + 1) / 2, 256, 0, st>>>(src, rows, dst, np);
+    gather_rows_kernel<<<(np + 7) / 8, 256, 0, st>>>(src, rows, dst, np);
     k_count_add(1);
 }
 #ifdef UMMA_TRACE

@@ -111,28 +111,45 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const uint16_t *__re
 #pragma unroll
         for (int c = 0; c < TE; c++) acc[a][c] = 0.0f;
 
+    // this thread's share of a 128-column chunk, fetched one chunk ahead of the arithmetic
+    constexpr int NH = (BT * (RT_KC / 4) + 255) / 256, NW = (BE * (RT_KC / 8) + 255) / 256;
+    float4 ph[NH]; uint4 pw[NW];
+    auto fetch = [&](int c0) {
+#pragma unroll
+        for (int k = 0; k < NH; k++) {
+            const int i = tid + 256 * k, r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
+            ph[k] = (i < BT * (RT_KC / 4) && b0 + r < nb) ? *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < NW; k++) {
+            const int i = tid + 256 * k, r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
+            pw[k] = (i < BE * (RT_KC / 8)) ? *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    fetch(0);
     for (int c0 = 0; c0 < HID; c0 += RT_KC) {
         __syncthreads();
-        // hidden tile: BT rows x 128 fp32, float4 per access
-        for (int i = tid; i < BT * (RT_KC / 4); i += 256) {
-            int r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (b0 + r < nb) v = *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c);
-            float *d = hs + r * RT_ROW + (c >> 3);
-            int jj = c & 7;
-            d[(jj + 0) * RT_LS] = v.x; d[(jj + 1) * RT_LS] = v.y; d[(jj + 2) * RT_LS] = v.z; d[(jj + 3) * RT_LS] = v.w;
+#pragma unroll
+        for (int k = 0; k < NH; k++) {
+            const int i = tid + 256 * k, r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
+            if (i < BT * (RT_KC / 4)) {
+                float *d = hs + r * RT_ROW + (c >> 3); const int jj = c & 7;
+                d[(jj + 0) * RT_LS] = ph[k].x; d[(jj + 1) * RT_LS] = ph[k].y; d[(jj + 2) * RT_LS] = ph[k].z; d[(jj + 3) * RT_LS] = ph[k].w;
+            }
         }
-        // router tile: BE rows x 128 bf16, eight per access
-        for (int i = tid; i < BE * (RT_KC / 8); i += 256) {
-            int r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
-            uint4 v = *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c);
-            float *d = ws + r * RT_ROW + (c >> 3);
-            d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
-            d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
-            d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
-            d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
+#pragma unroll
+        for (int k = 0; k < NW; k++) {
+            const int i = tid + 256 * k, r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
+            if (i < BE * (RT_KC / 8)) {
+                float *d = ws + r * RT_ROW + (c >> 3); const uint4 v = pw[k];
+                d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
+                d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
+                d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
+                d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
+            }
         }
         __syncthreads();
+        if (c0 + RT_KC < HID) fetch(c0 + RT_KC);
 #pragma unroll
         for (int i4 = 0; i4 < RT_KC / 8 / 4; i4++) {
             float4 hv[TT], wv[TE];
@@ -320,11 +337,10 @@ extern "C" void k_topk(cudaStream_t st, const float *logits, int *top, float *to
 // ------------------------------------------------------------------------------------------------------------
 // Grouping (maple.c:924-938) and tp (maple.c:1018-1019), deterministic without ordered atomics:
 //   1. mark:  bit b of mask[e] is set when token b chose expert e (atomicOr: the result does not depend on order)
-//   2. scan:  one CTA, thread e counts its bits; used experts are numbered in ascending order (NU, UE, USTART)
-//             and the tile lists for the grouped GEMMs are written
-//   3. fill:  one warp per expert walks its bits in token order: pair slot = USTART[u] + rank; UTOK, UW, and the
-//             slot of every (token, choice)
-//   4. tp:    per token the eight slots sorted ascending (pair index order = expert order)
+//   2. scan:  used experts are numbered in ascending order (NU, UE, USTART), the tile lists for the grouped GEMMs are
+//             written, and for every expert and 32-token word the slot of the word's first token
+//   3. place: one thread per token: pair slot = word prefix + rank inside the word; UTOK, UW, the slot of every
+//             (token, choice), and tp = the token's eight slots sorted ascending (pair index order = expert order)
 // ------------------------------------------------------------------------------------------------------------
 __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restrict__ mask, int mask_words, int np) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -333,17 +349,17 @@ __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restr
     atomicOr(&mask[(size_t)e * mask_words + (b >> 5)], 1u << (b & 31));
     atomicAdd(&mask[(size_t)NEXP * mask_words + e], 1u);        // pairs per expert, kept behind the bit rows (integer adds: any order, same sum)
 }
+// scan + word prefixes: 32 CTAs of 256 threads.  Every CTA repeats the scan over the 256 experts (cheap) so that its eight warps
+// know where their experts start; CTA 0 alone writes the compact lists and the tiles.  Warp w of CTA c then takes expert 8c + w and
+// writes, for every 32-token word of its bit row, how many of its tokens come before that word.
 __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__restrict__ mask, int mask_words, int *__restrict__ nu_out,
                                                           int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart, int *__restrict__ ecnt,
                                                           MoeTile *__restrict__ ta, int *__restrict__ nta, int tna,
-                                                          MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb) {
-    __shared__ int s_cnt[NEXP], s_used[NEXP], s_ta[NEXP], s_tb[NEXP];
-    __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
+                                                          MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb, int *__restrict__ wprefix) {
+    __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8], s_start[NEXP];
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
     const int cnt = (int)mask[(size_t)NEXP * mask_words + e];
-    if (ecnt) ecnt[e] = cnt;
-    int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
-    // inclusive warp scans of the four quantities
+    const int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
     int c = cnt, u = used, a = na, b = nb_;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -355,53 +371,51 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
     __syncthreads();
     int oc = 0, ou = 0, oa = 0, ob = 0;
     for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
-    s_cnt[e] = oc + c - cnt; s_used[e] = ou + u - used; s_ta[e] = oa + a - na; s_tb[e] = ob + b - nb_;   // exclusive
-    const int start = s_cnt[e], uidx = s_used[e];
-    estart[e] = used ? start : -1;
-    if (used) {
-        ue[uidx] = e; ustart[uidx] = start;
-        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * tna, min(tna, cnt - t * tna), e}; ta[s_ta[e] + t] = m; }
-        for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * tnb, min(tnb, cnt - t * tnb), e}; tb[s_tb[e] + t] = m; }
+    const int start = oc + c - cnt, uidx = ou + u - used, ta0 = oa + a - na, tb0 = ob + b - nb_;
+    s_start[e] = start;
+    if (blockIdx.x == 0) {
+        if (ecnt) ecnt[e] = cnt;
+        estart[e] = used ? start : -1;
+        if (used) {
+            ue[uidx] = e; ustart[uidx] = start;
+            for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * tna, min(tna, cnt - t * tna), e}; ta[ta0 + t] = m; }
+            for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * tnb, min(tnb, cnt - t * tnb), e}; tb[tb0 + t] = m; }
+        }
+        if (e == NEXP - 1) { const int nu = uidx + used; *nu_out = nu; ustart[nu] = start + cnt; *nta = ta0 + na; *ntb = tb0 + nb_; }
     }
-    if (e == NEXP - 1) {
-        int nu = uidx + used;
-        *nu_out = nu; ustart[nu] = start + cnt; *nta = s_ta[e] + na; *ntb = s_tb[e] + nb_;
-    }
-}
-__global__ void __launch_bounds__(256) group_fill_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ estart,
-                                                         const int *__restrict__ top, const float *__restrict__ topw,
-                                                         int *__restrict__ utok, float *__restrict__ uw, int *__restrict__ slot, int *__restrict__ uexp) {
-    const int lane = threadIdx.x & 31, e = blockIdx.x * 8 + (threadIdx.x >> 5);
-    int base = estart[e];
-    if (base < 0) return;
+    __syncthreads();
+    const int ex = blockIdx.x * 8 + wid;                     // this warp's expert
+    int run = s_start[ex];
     for (int w0 = 0; w0 < mask_words; w0 += 32) {
-        unsigned m = (w0 + lane < mask_words) ? mask[(size_t)e * mask_words + w0 + lane] : 0u;
-        int c = __popc(m), incl = c;
+        const int w = w0 + lane;
+        const int pc = w < mask_words ? __popc(mask[(size_t)ex * mask_words + w]) : 0;
+        int incl = pc;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-        int r = base + incl - c;
-        while (m) {
-            int bit = __ffs(m) - 1; m &= m - 1;
-            int b = (w0 + lane) * 32 + bit, s = 0;
-#pragma unroll
-            for (int k = 0; k < TOPK; k++) if (top[b * TOPK + k] == e) s = k;
-            utok[r] = b; uw[r] = topw[b * TOPK + s]; slot[b * TOPK + s] = r; if (uexp) uexp[r] = e; r++;
-        }
-        base += __shfl_sync(0xffffffffu, incl, 31);
+        if (w < mask_words) wprefix[(size_t)ex * mask_words + w] = run + incl - pc;       // slot of the word's first token
+        run += __shfl_sync(0xffffffffu, incl, 31);
     }
 }
-__global__ void group_tp_kernel(const int *__restrict__ slot, int *__restrict__ tp, int nb) {
-    int b = blockIdx.x * blockDim.x + threadIdx.x;
+// one thread per token: the slot of each of its eight pairs = the word prefix + the rank inside the word; the pair lists and tp
+__global__ void __launch_bounds__(128) group_place_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ wprefix,
+                                                          const int *__restrict__ top, const float *__restrict__ topw, int *__restrict__ utok,
+                                                          float *__restrict__ uw, int *__restrict__ slot, int *__restrict__ uexp, int *__restrict__ tp, int nb) {
+    const int b = blockIdx.x * 128 + threadIdx.x;
     if (b >= nb) return;
-    int s[TOPK];
+    const int w = b >> 5; const unsigned below = (1u << (b & 31)) - 1u;
+    int sl[TOPK];
 #pragma unroll
-    for (int k = 0; k < TOPK; k++) s[k] = slot[b * TOPK + k];
+    for (int k = 0; k < TOPK; k++) {
+        const int e = top[b * TOPK + k];
+        const int r = wprefix[(size_t)e * mask_words + w] + __popc(mask[(size_t)e * mask_words + w] & below);
+        sl[k] = r; slot[b * TOPK + k] = r; utok[r] = b; uw[r] = topw[b * TOPK + k]; if (uexp) uexp[r] = e;
+    }
 #pragma unroll
     for (int i = 1; i < TOPK; i++)
 #pragma unroll
-        for (int k = TOPK - 1; k >= 1; k--) if (k >= i && s[k] < s[k - 1]) { int t = s[k]; s[k] = s[k - 1]; s[k - 1] = t; }
+        for (int k = TOPK - 1; k >= 1; k--) if (k >= i && sl[k] < sl[k - 1]) { int x = sl[k]; sl[k] = sl[k - 1]; sl[k - 1] = x; }
 #pragma unroll
-    for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = s[k];
+    for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = sl[k];
 }
 // Decode batches (up to 256 tokens = 2048 pairs): the whole grouping in one CTA, so that the step costs one launch instead of
 // five.  Thread e owns expert e: it walks the pairs in token order (the table sits in shared memory), which gives the reference's
@@ -460,11 +474,11 @@ extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     const int np = g->nb * TOPK;
     cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit rows + the 256 counters behind them
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
-    group_scan_kernel<<<1, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
-                                          g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b);
-    group_fill_kernel<<<NEXP / 8, 256, 0, st>>>(g->mask, g->mask_words, g->estart, g->top, g->topw, g->utok, g->uw, g->slot, g->uexp);
-    group_tp_kernel<<<(g->nb + 127) / 128, 128, 0, st>>>(g->slot, g->tp, g->nb);
-    g_launches += 4;
+    int *wprefix = reinterpret_cast<int *>(g->mask + (size_t)NEXP * g->mask_words + NEXP);    // behind the bit rows and the counters
+    group_scan_kernel<<<NEXP / 8, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
+                                                 g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b, wprefix);
+    group_place_kernel<<<(g->nb + 127) / 128, 128, 0, st>>>(g->mask, g->mask_words, wprefix, g->top, g->topw, g->utok, g->uw, g->slot, g->uexp, g->tp, g->nb);
+    g_launches += 3;
 }
 
 // ------------------------------------------------------------------------------------------------------------

@@ -45,7 +45,7 @@ void k_router_logits(cudaStream_t st, const uint16_t *router, const float *hn, c
 void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb);
 typedef struct {
     const int *top; const float *topw; int nb;
-    unsigned *mask;          /* [256][mask_words] bit rows, then 256 counters */
+    unsigned *mask;          /* [256][mask_words] bit rows, then 256 counters, then [256][mask_words] word prefixes */
     int mask_words;
     int *nu, *ue, *estart, *ustart, *utok, *slot, *tp; float *uw;
     int *ecnt, *uexp;        /* optional: pairs per expert [256], expert of every pair [np] (expert parallel) */

@@ -6,7 +6,7 @@
 // file offers one entry point, gmoe_group_noalloc, that does the same work as the library's grouping stage but keeps
 // its scratch in a fixed array that is part of the loaded module instead of in buffers obtained from cudaMalloc.
 //
-// The scratch (NA_SCRATCH_BYTES, about 205 KB) exists once per GPU that loads the library and stays until the
+// The scratch (NA_SCRATCH_BYTES, about 270 KB) exists once per GPU that loads the library and stays until the
 // process exits.  It bounds the call: at most NA_MAXTOK = 2048 tokens.  Every call uses the same array and finds
 // the previous call's contents in it; the part that has to start at zero (the token bit masks) is cleared on the
 // caller's stream at the start of each call.  Two calls that overlap on the GPU (different streams, or different
@@ -22,7 +22,7 @@
 #define NA_TILES (NA_MAXTOK * 8 / 8 + 256)
 
 struct NaScratch {
-    unsigned mask[256 * NA_WORDS + 256]; // bit b of row e: token b chose expert e, then one counter per expert (must be zero at the start of a call)
+    unsigned mask[2 * 256 * NA_WORDS + 256]; // bit b of row e: token b chose expert e, one counter per expert (both zero at the start of a call), word prefixes
     int estart[256];
     int slot[NA_MAXTOK * 8];
     MoeTile tiles_a[NA_TILES], tiles_b[NA_TILES];
