@@ -38,13 +38,14 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
+typedef struct { uint16_t *router, *post_ln; void *router_t; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
 
 static struct {
     int ready, maxtok, maxp, mask_words, keep, path, nb_cur, ep_on;
     cudaStream_t st; cudaEvent_t e0, e1;
     void *reg[MAXREG]; size_t reg_len[MAXREG]; int nreg; double blit_s;
     LayerDev ly[GMOE_LAYERS];
+    void *hT;                  /* hidden rows in the tile router's layout */
     float *x, *hn, *y, *hqs, *logits, *topw, *uw, *act, *aqs, *down, *gate, *up, *bias;
     int8_t *hq, *aq;
     int *ecnt, *uexp, *hqsum, *top, *nu, *ue, *estart, *ustart, *utok, *slot, *tp, *aqsum, *ntiles_a, *ntiles_b, *gu_dots, *dn_dots;
@@ -105,7 +106,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     CU(who, cudaEventCreate(&S.e0)); CU(who, cudaEventCreate(&S.e1));
     size_t P = (size_t)maxtok * TOPK, T = (size_t)maxtok;
     S.maxtok = maxtok; S.maxp = (int)P; S.mask_words = (maxtok + 31) / 32;
-    ALLOC(x, T * HID * 4); ALLOC(hn, T * HID * 4); ALLOC(y, T * HID * 4);
+    ALLOC(x, T * HID * 4); ALLOC(hn, T * HID * 4); ALLOC(y, T * HID * 4); ALLOC(hT, (T + 31) / 32 * 32 * HID * 4);
     ALLOC(hq, T * HID); ALLOC(hqs, T * 4); ALLOC(hqsum, T * 4);
     ALLOC(logits, T * NEXP * 4); ALLOC(top, P * 4); ALLOC(topw, P * 4); ALLOC(bias, NEXP * 4);
     ALLOC(ecnt, NEXP * 4); ALLOC(uexp, P * 4);
@@ -192,7 +193,7 @@ static int layer_bufs(const char *who, int L) {
     if (L < 0 || L >= GMOE_LAYERS) return fail(who, "layer %d outside 0..%d", L, GMOE_LAYERS - 1);
     LayerDev *l = &S.ly[L];
     if (!l->router) {
-        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->post_ln, HID * 2) ||
+        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->post_ln, HID * 2) ||
             dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs)) || dmalloc((void **)&l->maps, NEXP * sizeof(ExpertMaps)))
             return fail(who, "out of device memory for layer %d", L);
     }
@@ -206,6 +207,7 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     CU("gmoe", cudaMemcpyAsync(l->maps, S.h_maps, NEXP * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     uint16_t ones[HID]; for (int i = 0; i < HID; i++) ones[i] = 0x3F80;
     CU("gmoe", cudaMemcpyAsync(l->router, router, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st));
+    k_router_pack(S.st, l->router, l->router_t);
     CU("gmoe", cudaMemcpyAsync(l->post_ln, post_ln ? post_ln : ones, HID * 2, cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st));
@@ -231,6 +233,7 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     if (!r) return fail("gmoe", "out of host memory");
     msynth_router(seed, L, r); msynth_norm(seed, L, nw);
     cudaError_t e1 = cudaMemcpyAsync(l->router, r, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st);
+    k_router_pack(S.st, l->router, l->router_t);
     cudaError_t e2 = cudaMemcpyAsync(l->post_ln, nw, HID * 2, cudaMemcpyHostToDevice, S.st);
     cudaError_t e3 = cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st);
     cudaError_t e4 = cudaStreamSynchronize(S.st);
@@ -320,11 +323,17 @@ static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int
     }
     if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6); }
 }
+/* router logits: batches past the decode sizes take the tiled kernel on the re-laid router rows */
+#define ROUTER_TILE_MIN 257
+static void run_router(const LayerDev *l, const float *bias, int nb) {
+    if (nb >= ROUTER_TILE_MIN) k_router_logits_tile(S.st, l->router_t, S.hn, S.hT, bias, S.logits, nb, S.err);
+    else k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb);
+}
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {
     LayerDev *l = &S.ly[L];
     prof_begin(0); k_norm_prep(S.st, norm ? S.x : S.hn, norm ? l->post_ln : NULL, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
-    prof_begin(1); k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb); prof_end(1);
+    prof_begin(1); run_router(l, bias, nb); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3); run_group(nb); prof_end(3);
     run_experts(l->tab, l->maps, S.ue, nb, 7);
@@ -458,7 +467,7 @@ int gmoe_post_norm(int L, int nb, float *logits) {
     if (check_call("gmoe", L, nb)) return -1;
     LayerDev *l = &S.ly[L];
     k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb);
-    k_router_logits(S.st, l->router, S.hn, NULL, S.logits, nb);
+    run_router(l, NULL, nb);
     if (logits) CU("gmoe", cudaMemcpyAsync(logits, S.logits, (size_t)nb * NEXP * 4, cudaMemcpyDeviceToHost, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st));
     return 0;
@@ -589,8 +598,8 @@ int gmoe_stage(const char *name, int L, int nb) {
     cudaEventRecord(S.e0, S.st);
     if (!strcmp(name, "norm")) k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb);
     else if (!strcmp(name, "prep")) k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
-    else if (!strcmp(name, "router")) k_router_logits(S.st, l->router, S.hn, NULL, S.logits, nb);
-    else if (!strcmp(name, "router_bias")) k_router_logits(S.st, l->router, S.hn, S.bias, S.logits, nb);
+    else if (!strcmp(name, "router")) run_router(l, NULL, nb);
+    else if (!strcmp(name, "router_bias")) run_router(l, S.bias, nb);
     else if (!strcmp(name, "topk")) k_topk(S.st, S.logits, S.top, S.topw, nb);
     else if (!strcmp(name, "group")) run_group(nb);
     else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, S.ue, nb, 1); }
@@ -738,7 +747,7 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     LayerDev *l = &S.ly[L];
     const int tn = tile_tn(nb), um = use_umma(nb);
     prof_begin(0); k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
-    prof_begin(1); k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb); prof_end(1);
+    prof_begin(1); run_router(l, bias, nb); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3);
     run_group(nb);
