@@ -106,7 +106,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     CU(who, cudaEventCreate(&S.e0)); CU(who, cudaEventCreate(&S.e1));
     size_t P = (size_t)maxtok * TOPK, T = (size_t)maxtok;
     S.maxtok = maxtok; S.maxp = (int)P; S.mask_words = (maxtok + 31) / 32;
-    ALLOC(x, T * HID * 4); ALLOC(hn, T * HID * 4); ALLOC(y, T * HID * 4); ALLOC(hT, (T + 31) / 32 * 32 * HID * 4);
+    ALLOC(x, T * HID * 4); ALLOC(hn, T * HID * 4); ALLOC(y, T * HID * 4); ALLOC(hT, (T + 15) / 16 * 16 * HID * 8);
     ALLOC(hq, T * HID); ALLOC(hqs, T * 4); ALLOC(hqsum, T * 4);
     ALLOC(logits, T * NEXP * 4); ALLOC(top, P * 4); ALLOC(topw, P * 4); ALLOC(bias, NEXP * 4);
     ALLOC(ecnt, NEXP * 4); ALLOC(uexp, P * 4);

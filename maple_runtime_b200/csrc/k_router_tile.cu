@@ -3,8 +3,8 @@
 // logit[b][e] = hsum over eight lanes of ( sum_i W[e][8i+l] * hn[b][8i+l] ), each lane one chain of fused multiply-adds in
 // increasing i, the lanes added as ((l0+l4)+(l1+l5))+((l2+l6)+(l3+l7)) (maple.c:117-121): the same bits as the CPU path.
 //
-// A CTA owns 32 tokens x 128 experts.  Eight arithmetic warps hold 8 lanes x 32 positions; a position is an
-// 8-token x 16-expert register tile, so one step of a lane costs 64 bytes of shared-memory reads (eight fp32 hidden values,
+// A CTA owns up to 32 tokens x 128 experts.  Eight warps hold 8 lanes x 32 positions; a position is an
+// 8-token (fewer when that fills the SMs better) x 16-expert register tile, so one step of a lane costs 64 bytes of shared-memory reads (eight fp32 hidden values,
 // sixteen bf16 weights) for 128 multiply-adds: half a byte per multiply-add, half of what the load path delivers at the full
 // multiply-add rate.  The multiply-adds are issued two at a time (fma.rn.f32x2, each half an IEEE fused multiply-add).
 // Both operands come from copies laid out for exactly this access: per 128-column chunk and 8-token (16-expert) group,
@@ -41,14 +41,15 @@ __global__ void __launch_bounds__(256) router_pack_w_kernel(const uint16_t *__re
         v[m] = (uint32_t)W[(size_t)(e + 2 * m) * HID + col] | ((uint32_t)W[(size_t)(e + 2 * m + 1) * HID + col] << 16);
     WT[o] = make_uint4(v[0], v[1], v[2], v[3]);
 }
-// normalised hidden rows (fp32 [nb][2048]) -> [tile of 32 tokens][chunk][group of 8][i][h][j][4 tokens]; rows past nb read as zero
-__global__ void __launch_bounds__(256) router_pack_h_kernel(const float *__restrict__ hn, float4 *__restrict__ hT, int nb) {
+// normalised hidden rows (fp32 [nb][2048]) -> [tile of 4*tt tokens][chunk][group of tt tokens in 8 slots][i][h][j][4 slots];
+// slots past tt and rows past nb read as zero
+__global__ void __launch_bounds__(256) router_pack_h_kernel(const float *__restrict__ hn, float4 *__restrict__ hT, int nb, int tt) {
     const int o = blockIdx.x * 256 + threadIdx.x;
     const int j = o & 7, h = (o >> 3) & 1, i = (o >> 4) & 15, tg = (o >> 8) & 3, ch = (o >> 10) & 15, tile = o >> 14;
-    const int t0 = tile * RP_TOK + tg * 8 + h * 4, col = (ch * RP_KI + i) * 8 + j;
+    const int t0 = tile * 4 * tt + tg * tt, col = (ch * RP_KI + i) * 8 + j;
     float v[4];
 #pragma unroll
-    for (int m = 0; m < 4; m++) v[m] = (t0 + m < nb) ? hn[(size_t)(t0 + m) * HID + col] : 0.0f;
+    for (int m = 0; m < 4; m++) v[m] = (h * 4 + m < tt && t0 + h * 4 + m < nb) ? hn[(size_t)(t0 + h * 4 + m) * HID + col] : 0.0f;
     hT[o] = make_float4(v[0], v[1], v[2], v[3]);
 }
 
@@ -65,6 +66,7 @@ __device__ __forceinline__ void fma2(uint64_t &acc, uint64_t a, uint64_t b) {
 
 struct RpBars { uint64_t full[RP_STAGES], empty[RP_STAGES]; int abort; };
 
+template <int TT>
 __global__ void __maxnreg__(224) router_tile_kernel(const uint8_t *__restrict__ WT, const uint8_t *__restrict__ hT,
                                                             const float *__restrict__ bias, float *__restrict__ logits, int nb, int *err) {
     extern __shared__ __align__(128) uint8_t rp_ring[];
@@ -91,9 +93,9 @@ __global__ void __maxnreg__(224) router_tile_kernel(const uint8_t *__restrict__ 
         };
         if (tid == 0) for (int ch = 0; ch < RP_STAGES - 1; ch++) issue(ch);
         const int j = tid & 7, tg = (tid >> 3) & 3, eg = warp;      // the four positions of a warp share their sixteen experts
-        uint64_t acc[8][8];                                           // [token][expert pair], halves = experts 2m, 2m+1
+        uint64_t acc[TT][8];                                          // [token][expert pair], halves = experts 2m, 2m+1
 #pragma unroll
-        for (int a = 0; a < 8; a++)
+        for (int a = 0; a < TT; a++)
 #pragma unroll
             for (int m = 0; m < 8; m++) acc[a][m] = 0ull;
         bool live = true;
@@ -116,9 +118,9 @@ __global__ void __maxnreg__(224) router_tile_kernel(const uint8_t *__restrict__ 
 #pragma unroll
                 for (int m = 0; m < 8; m++) wv[m] = pair64(wu[m] << 16, wu[m] & 0xFFFF0000u);
 #pragma unroll
-                for (int a = 0; a < 8; a++) hh[a] = pair64(__float_as_uint(hv[a]), __float_as_uint(hv[a]));
+                for (int a = 0; a < TT; a++) hh[a] = pair64(__float_as_uint(hv[a]), __float_as_uint(hv[a]));
 #pragma unroll
-                for (int a = 0; a < 8; a++)
+                for (int a = 0; a < TT; a++)
 #pragma unroll
                     for (int m = 0; m < 8; m++) fma2(acc[a][m], wv[m], hh[a]);
             }
@@ -127,12 +129,12 @@ __global__ void __maxnreg__(224) router_tile_kernel(const uint8_t *__restrict__ 
         }
         if (live) {
             // every lane ends with the full sums (the additions commute pairwise); lane j stores token j's sixteen logits
-            const int e0 = eb * RP_EXP + eg * 16, b0 = tile * RP_TOK + tg * 8;
+            const int e0 = eb * RP_EXP + eg * 16, b0 = tile * 4 * TT + tg * TT;
             float bv[16];
 #pragma unroll
             for (int c = 0; c < 16; c++) bv[c] = bias ? bias[e0 + c] : 0.0f;
 #pragma unroll
-            for (int a = 0; a < 8; a++) {
+            for (int a = 0; a < TT; a++) {
                 float l[16];
 #pragma unroll
                 for (int m = 0; m < 8; m++) { l[2 * m] = __uint_as_float((uint32_t)acc[a][m]); l[2 * m + 1] = __uint_as_float((uint32_t)(acc[a][m] >> 32)); }
@@ -160,12 +162,35 @@ extern "C" void k_router_pack(cudaStream_t st, const uint16_t *router, void *rou
     router_pack_w_kernel<<<NEXP * HID / 8 / 256, 256, 0, st>>>(router, (uint4 *)router_t);
     k_count_add(1);
 }
+static int g_force_tt = 0;
+// tests: pin the tokens per thread (4..8; 0 = choose by batch size)
+extern "C" void k_router_tile_force(int tt) { g_force_tt = (tt >= 4 && tt <= 8) ? tt : 0; }
+template <int TT>
+static void launch_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err) {
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(router_tile_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, RP_SMEM); attr_done = true; }
+    const int tiles = (nb + 4 * TT - 1) / (4 * TT);
+    router_pack_h_kernel<<<tiles * 64, 256, 0, st>>>(hn, (float4 *)hT, nb, TT);
+    router_tile_kernel<TT><<<dim3(NEXP / RP_EXP, tiles), 256, RP_SMEM, st>>>((const uint8_t *)router_t, (const uint8_t *)hT, bias, logits, nb, err);
+}
+// A thread's tile is tt tokens x 16 experts, a CTA's 4*tt tokens x 128 experts; tt in 4..8 is chosen so that the CTAs fill whole
+// waves of the SMs with the least arithmetic per wave (2048 tokens: tt = 7, 148 CTAs).  hT must hold ceil(nb/16) * 256 KB.
 extern "C" void k_router_logits_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err) {
     if (nb <= 0) return;
-    const int tiles = (nb + RP_TOK - 1) / RP_TOK;
-    static bool attr_done = false;
-    if (!attr_done) { cudaFuncSetAttribute(router_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RP_SMEM); attr_done = true; }
-    router_pack_h_kernel<<<tiles * 64, 256, 0, st>>>(hn, (float4 *)hT, nb);
-    router_tile_kernel<<<dim3(NEXP / RP_EXP, tiles), 256, RP_SMEM, st>>>((const uint8_t *)router_t, (const uint8_t *)hT, bias, logits, nb, err);
+    static int sms = 0;
+    if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms < 1) sms = 148; }
+    int best = 8; long cost = -1;
+    for (int tt = 8; tt >= 4 && !g_force_tt; tt--) {
+        const long ctas = 2L * ((nb + 4 * tt - 1) / (4 * tt)), c = ((ctas + sms - 1) / sms) * (tt * 8 + 5);   /* 5: the per-step cost that does not shrink with tt */
+        if (cost < 0 || c < cost) { cost = c; best = tt; }
+    }
+    if (g_force_tt) best = g_force_tt;
+    switch (best) {
+    case 4: launch_tile<4>(st, router_t, hn, hT, bias, logits, nb, err); break;
+    case 5: launch_tile<5>(st, router_t, hn, hT, bias, logits, nb, err); break;
+    case 6: launch_tile<6>(st, router_t, hn, hT, bias, logits, nb, err); break;
+    case 7: launch_tile<7>(st, router_t, hn, hT, bias, logits, nb, err); break;
+    default: launch_tile<8>(st, router_t, hn, hT, bias, logits, nb, err); break;
+    }
     k_count_add(2);
 }

@@ -80,6 +80,27 @@ def test_layer_all_stages_equal_oracle(nb, stream, norm, layers, oracle, weights
     assert same_bits(got, want), f"rel {rel(got, want):.3e}"
 
 
+@pytest.mark.parametrize("nb,tt", [(257, 0), (300, 5), (999, 0), (1300, 0), (1301, 6), (1600, 0), (2048, 0), (2047, 8), (1111, 7), (640, 4)])
+def test_tiled_router_equals_oracle_for_every_tile_size(nb, tt, layers, clib, oracle, weights):
+    """Batches past the decode sizes take the tiled router kernel; a thread's tile holds 4..8 tokens (tt, 0 = chosen by
+    batch size).  Ragged last tiles, every tile size, with and without the selection bias: logits bit for bit."""
+    g = layers
+    router, _, _ = weights.layer(2)
+    hn = weights.hidden(400 + tt, nb)
+    bias = np.linspace(-1.0, 1.0, 256).astype(np.float32)
+    want = oracle.router_logits(router, hn)
+    clib.k_router_tile_force(tt)
+    try:
+        g.poke("hn", hn)
+        g.stage("router", 2, nb)
+        assert same_bits(g.peek("logits", nb).reshape(nb, 256), want)
+        g.poke("bias", bias)
+        g.stage("router_bias", 2, nb)
+        assert same_bits(g.peek("logits", nb).reshape(nb, 256), want + bias[None, :])
+    finally:
+        clib.k_router_tile_force(0)
+
+
 @pytest.mark.parametrize("case", list(mg.CASES))
 def test_fixtures_from_the_reference(case, layers, clib):
     """The reference's own outputs (tests/golden) without the oracle in between."""
