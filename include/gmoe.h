@@ -64,18 +64,21 @@ int gmoe_post_norm(int L, int nb, float *logits);
 /* ---- expert parallelism across the GPUs of one NVLink box (no counterpart in the reference, which is single-device) ---- */
 /* One process per GPU.  Rank r keeps its own tokens and experts r*E .. (r+1)*E-1 (E = 256/world; gmoe_synth_layer or
  * gmoe_set_layer give each rank at least its own experts).  Set-up: rank 0 calls gmoe_ep_unique_id and hands the 128 bytes
- * to every rank; every rank calls gmoe_ep_init (after gmoe_init), then gmoe_ep_handles; the 320-byte results of all ranks,
+ * to every rank; every rank calls gmoe_ep_init (after gmoe_init), then gmoe_ep_handles; the 448-byte results of all ranks,
  * concatenated in rank order, go to gmoe_ep_connect on every rank.  Then gmoe_ep_forward* replace gmoe_forward*: same
  * arguments, same result bits, every rank calls them together with the same nb. */
 int gmoe_ep_unique_id(void *out128);
 int gmoe_ep_init(int rank, int world, const void *id128);
-int gmoe_ep_handles(void *out320);
+int gmoe_ep_handles(void *out448);
 int gmoe_ep_connect(const void *all_handles);
 /* chunk >= 0: start from chunk `chunk` of the ring (gmoe_chunks_upload); -1: from the device-resident hidden state */
 int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias);
 double gmoe_ep_forward(float *x, int nb, int l0, int nl, const float *bias);
 int gmoe_ep_allmax(double *v);            /* max over ranks (also a barrier) */
 int gmoe_ep_received(void);               /* pairs this rank's experts received in the last layer */
+/* The ranks meet through arrival flags in each other's memory; a wait longer than 10 s makes the call fail (code 41 in the
+ * message).  This runs such a wait with a missing peer and a limit of `ms` milliseconds on this GPU alone and returns the code. */
+int gmoe_ep_timeout_selftest(int ms);
 
 /* ---- parity hooks: named device buffers of the last call, and single stages ---------------------------------- */
 /* Names: x hn y hq hqs hqsum logits top topw nu ue ustart utok uw tp gate up act aq aqs aqsum down gu_dots dn_dots */

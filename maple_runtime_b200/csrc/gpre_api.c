@@ -38,7 +38,7 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; void *router_t; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
+typedef struct { uint16_t *router, *post_ln; void *router_t; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
 
 static struct {
     int ready, maxtok, maxp, mask_words, keep, path, nb_cur, ep_on;
@@ -46,6 +46,8 @@ static struct {
     void *reg[MAXREG]; size_t reg_len[MAXREG]; int nreg; double blit_s;
     LayerDev ly[GMOE_LAYERS];
     void *hT;                  /* hidden rows in the tile router's layout */
+    uint8_t *wire;             /* compact down rows of the tcgen05 path + their records (kernels.h WIRE_*) */
+    const float **dsp_call, *h_dsp[NEXP];   /* down-scale pointers of one gpre_moe call's experts; host staging */
     float *x, *hn, *y, *hqs, *logits, *topw, *uw, *act, *aqs, *down, *gate, *up, *bias;
     int8_t *hq, *aq;
     int *ecnt, *uexp, *hqsum, *top, *nu, *ue, *estart, *ustart, *utok, *slot, *tp, *aqsum, *ntiles_a, *ntiles_b, *gu_dots, *dn_dots;
@@ -86,9 +88,19 @@ static int tmap_bytes_2d(const char *who, TMap *out, const void *base, uint64_t 
     if (r != CUDA_SUCCESS) return fail(who, "cuTensorMapEncodeTiled failed (%d) for %p, %llu x %llu", (int)r, base, (unsigned long long)rows, (unsigned long long)width);
     return 0;
 }
+/* the down codes [2048 rows][128 bytes] seen as [1024 row pairs][2 parities][128 bytes]: a box of 128 row pairs at parity h is the
+ * even (h = 0) or odd (h = 1) rows of a 256-row block, which the tcgen05 down kernel puts into its two accumulators */
+static int tmap_down_3d(const char *who, TMap *out, const void *base) {
+    cuuint64_t gdim[3] = {128, 2, 1024}, gstride[2] = {128, 256};
+    cuuint32_t box[3] = {128, 1, 128}, estr[3] = {1, 1, 1};
+    CUresult r = g_encode((CUtensorMap *)out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(who, "cuTensorMapEncodeTiled failed (%d) for the down codes at %p", (int)r, base);
+    return 0;
+}
 static int expert_maps(const char *who, const ExpertPtrs *e, ExpertMaps *m) {
     if (tmap_bytes_2d(who, &m->gate, e->gc, 512, 512, 512, 128, 128) || tmap_bytes_2d(who, &m->up, e->uc, 512, 512, 512, 128, 128) ||
-        tmap_bytes_2d(who, &m->down, e->dc, 128, 2048, 128, 128, 128)) return -1;
+        tmap_down_3d(who, &m->down, e->dc)) return -1;
     return 0;
 }
 
@@ -116,6 +128,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(ntiles_a, 16); ALLOC(ntiles_b, 16);
     ALLOC(act, P * FFN * 4); ALLOC(gate, P * FFN * 4); ALLOC(up, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
     ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16); ALLOC(maps_call, NEXP * sizeof(ExpertMaps)); ALLOC(hq_sorted, P * HID);
+    ALLOC(wire, WIRE_BYTES(P)); CU(who, cudaMemset(S.wire, 0, WIRE_BYTES(P))); ALLOC(dsp_call, NEXP * sizeof(void *));
     if (tmap_init(who)) return -1;
     if (tmap_bytes_2d(who, &S.bmap_hq, S.hq_sorted, HID, P, HID, 128, UMMA_TN) || tmap_bytes_2d(who, &S.bmap_aq, S.aq, FFN, P, FFN, 128, UMMA_TN)) return -1;
     CU(who, cudaMemset(S.err, 0, 16));
@@ -193,7 +206,7 @@ static int layer_bufs(const char *who, int L) {
     if (L < 0 || L >= GMOE_LAYERS) return fail(who, "layer %d outside 0..%d", L, GMOE_LAYERS - 1);
     LayerDev *l = &S.ly[L];
     if (!l->router) {
-        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->post_ln, HID * 2) ||
+        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->dsp, NEXP * sizeof(void *)) || dmalloc((void **)&l->post_ln, HID * 2) ||
             dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs)) || dmalloc((void **)&l->maps, NEXP * sizeof(ExpertMaps)))
             return fail(who, "out of device memory for layer %d", L);
     }
@@ -210,6 +223,8 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     k_router_pack(S.st, l->router, l->router_t);
     CU("gmoe", cudaMemcpyAsync(l->post_ln, post_ln ? post_ln : ones, HID * 2, cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
+    for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
+    CU("gmoe", cudaMemcpyAsync(l->dsp, S.h_dsp, NEXP * sizeof(void *), cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st));
     l->set = 1; return 0;
 }
@@ -236,6 +251,8 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     k_router_pack(S.st, l->router, l->router_t);
     cudaError_t e2 = cudaMemcpyAsync(l->post_ln, nw, HID * 2, cudaMemcpyHostToDevice, S.st);
     cudaError_t e3 = cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st);
+    for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
+    if (e3 == cudaSuccess) e3 = cudaMemcpyAsync(l->dsp, S.h_dsp, NEXP * sizeof(void *), cudaMemcpyHostToDevice, S.st);
     cudaError_t e4 = cudaStreamSynchronize(S.st);
     free(r);
     if (e1 || e2 || e3 || e4) return fail("gmoe", "synthetic layer %d: %s", L, cudaGetErrorString(e1 ? e1 : e2 ? e2 : e3 ? e3 : e4));
@@ -292,7 +309,7 @@ static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const ExpertM
     if (use_umma(nb)) { a->tiles = S.tiles_b; a->ntiles = S.ntiles_b; a->max_tiles = nb * TOPK / UMMA_TN + NEXP; }
     else { a->tiles = S.tiles_a; a->ntiles = S.ntiles_a; a->max_tiles = nb * TOPK / tile_tn(nb) + NEXP; }
     a->hq = S.hq; a->hqs = S.hqs; a->hqsum = S.hqsum; a->act = S.act;
-    a->aq = S.aq; a->aqs = S.aqs; a->aqsum = S.aqsum; a->down = S.down;
+    a->aq = S.aq; a->aqs = S.aqs; a->aqsum = S.aqsum; a->down = S.down; a->wire = S.wire; a->wire_cap = S.maxp;
     if (S.keep || use_umma(nb)) { a->gate = S.gate; a->up = S.up; }          /* the tensor-core GEMM always stores gate and up */
     if (S.keep) { a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
 }
@@ -304,7 +321,8 @@ static void run_group(int nb) {
     k_group(S.st, &g);
     if (use_umma(nb) && !S.ep_on) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);   /* the permute: int8 rows into pair order for the TMA */
 }
-static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int *ue, int nb, int which) {   /* which: 1 gateup, 2 actq, 4 down */
+/* which: 1 gateup, 2 actq, 4 down; dsp: the down-scale pointers the tiles' expert indices name (the combine needs the same) */
+static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const float *const *dsp, const int *ue, int nb, int which) {
     ExpertArgs a; fill_expert_args(&a, tab, maps, ue, nb);
     int tn = tile_tn(nb);
     int um = use_umma(nb);
@@ -321,7 +339,17 @@ static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const int
         else k_actq(S.st, S.act, S.aq, S.aqs, S.aqsum, NULL, nb * TOPK);
         prof_end(5);
     }
-    if (which & 4) { prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6); }
+    if (which & 4) {
+        prof_begin(6);
+        if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn);
+        if (um && S.keep) k_wire_decode(S.st, S.wire, S.maxp, dsp, S.down, nb * TOPK);     /* fp32 rows for stage comparisons */
+        prof_end(6);
+    }
+}
+/* weighted combine of the pairs' down rows into out (init + sum): compact rows after the tcgen05 kernel, fp32 rows otherwise */
+static void run_combine(const float *const *dsp, int nb, const float *init, float *out) {
+    if (use_umma(nb)) k_combine_wire(S.st, S.wire, S.maxp, dsp, S.uw, S.tp, init, out, nb);
+    else k_combine(S.st, S.down, S.uw, S.tp, init, out, nb);
 }
 /* router logits: batches past the decode sizes take the tiled kernel on the re-laid router rows */
 #define ROUTER_TILE_MIN 257
@@ -336,9 +364,9 @@ static void run_layer(int L, int nb, int norm, const float *bias) {
     prof_begin(1); run_router(l, bias, nb); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3); run_group(nb); prof_end(3);
-    run_experts(l->tab, l->maps, S.ue, nb, 7);
+    run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 7);
     prof_begin(7);
-    if (norm) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb); else k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
+    if (norm) run_combine((const float *const *)l->dsp, nb, S.x, S.x); else run_combine((const float *const *)l->dsp, nb, NULL, S.y);
     prof_end(7);
 }
 static int check_call(const char *who, int L, int nb) {
@@ -356,8 +384,11 @@ static double finish(const char *who) {
     cudaMemcpyAsync(S.h_err, S.err, 4, cudaMemcpyDeviceToHost, S.st);
     cudaError_t e = cudaStreamSynchronize(S.st);
     if (e == cudaSuccess && *S.h_err) {
+        const int code = *S.h_err;
         *S.h_err = 0; cudaMemsetAsync(S.err, 0, 4, S.st);
-        fail(who, "a kernel gave up waiting on a barrier (bounded wait ran out); results are invalid"); return -1.0;
+        fail(who, "a kernel gave up waiting (code %d: %s); results are invalid", code,
+             code == 41 ? "a rank did not arrive at the expert-parallel rendezvous" : code == 31 ? "router operand ring" : "barrier inside an expert kernel");
+        return -1.0;
     }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { fail(who, "%s", cudaGetErrorString(e)); return -1.0; }
@@ -504,6 +535,8 @@ static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc,
     }
     for (int a = 0; a < np; a++) if (ptok[a] < 0 || ptok[a] >= nb) return fail(who, "ptok[%d] = %d", a, ptok[a]);
     for (int i = 0; i < np; i++) if (tp[i] < 0 || tp[i] >= np) return fail(who, "tp[%d] = %d", i, tp[i]);
+    for (int u = 0; u < NEXP; u++) S.h_dsp[u] = u < nu ? S.h_tab[u].ds : NULL;
+    CU(who, cudaMemcpyAsync(S.dsp_call, S.h_dsp, NEXP * sizeof(void *), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.tab_call, S.h_tab, (size_t)nu * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.maps_call, S.h_maps, (size_t)nu * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     CU(who, cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
@@ -526,8 +559,8 @@ double gpre_moe(const float *x, int nb, int nu, const uint32_t *loc, const int *
     cudaEventRecord(S.e0, S.st);
     k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
     if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);
-    run_experts(S.tab_call, S.maps_call, NULL, nb, 7);
-    k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
+    run_experts(S.tab_call, S.maps_call, (const float *const *)S.dsp_call, NULL, nb, 7);
+    run_combine((const float *const *)S.dsp_call, nb, NULL, S.y);
     cudaEventRecord(S.e1, S.st);
     CUD("gpre", cudaMemcpyAsync(y, S.y, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
     S.nb_cur = nb;
@@ -543,8 +576,8 @@ void gfull_moe(int nu, const uint32_t *loc, const int *regs, const int *ustart, 
     if (upload_grouping("gfull", nb, nu, loc, regs, ustart, ptok, pw, tp)) return;
     cudaEventRecord(S.e0, S.st);
     if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);
-    run_experts(S.tab_call, S.maps_call, NULL, nb, 7);            /* hq/hqs/hqsum were left by gmoe_post_norm */
-    k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
+    run_experts(S.tab_call, S.maps_call, (const float *const *)S.dsp_call, NULL, nb, 7);            /* hq/hqs/hqsum were left by gmoe_post_norm */
+    run_combine((const float *const *)S.dsp_call, nb, S.x, S.x);
     cudaEventRecord(S.e1, S.st);
     S.fwd_timed = 1;
 }
@@ -602,11 +635,11 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "router_bias")) run_router(l, S.bias, nb);
     else if (!strcmp(name, "topk")) k_topk(S.st, S.logits, S.top, S.topw, nb);
     else if (!strcmp(name, "group")) run_group(nb);
-    else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, S.ue, nb, 1); }
-    else if (!strcmp(name, "actq")) run_experts(l->tab, l->maps, S.ue, nb, 2);
-    else if (!strcmp(name, "down")) run_experts(l->tab, l->maps, S.ue, nb, 4);
-    else if (!strcmp(name, "combine_y")) k_combine(S.st, S.down, S.uw, S.tp, NULL, S.y, nb);
-    else if (!strcmp(name, "combine_x")) k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
+    else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 1); }
+    else if (!strcmp(name, "actq")) run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 2);
+    else if (!strcmp(name, "down")) run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 4);
+    else if (!strcmp(name, "combine_y")) run_combine((const float *const *)l->dsp, nb, NULL, S.y);
+    else if (!strcmp(name, "combine_x")) run_combine((const float *const *)l->dsp, nb, S.x, S.x);
     else return fail("gmoe", "no stage named %s", name);
     cudaEventRecord(S.e1, S.st);
     return finish("gmoe") < 0 ? -1 : 0;
@@ -660,11 +693,12 @@ void gpux_end_multi(void *h, float *out, int np) { (void)h; (void)out; (void)np;
 /* ================================================================================================================
  * Expert parallelism across the GPUs of one NVLink box (one process per GPU).  The reference has no counterpart
  * (single process, single device).  Rank r keeps its own tokens and the experts r*E .. (r+1)*E-1, E = 256 / world.
- * Per layer: local norm / router / top-8 / grouping -> all-gather of the per-expert pair counts (NCCL) -> every rank
- * stores its int8 rows straight into the owners' receive buffers (k_ep.cu, peer stores over NVLink) -> barrier ->
- * the owners run gate+up, SiLU+int8 and down on what they received, the down epilogue stores each result row
- * straight into the token's rank -> barrier -> local combine, in the same order as on one GPU, so the hidden state
- * is the same bits as without expert parallelism.  NCCL carries only the 1 KB count exchange and the barriers.
+ * Per layer: local norm / router / top-8 / grouping -> exchange of the per-expert pair counts (peer stores and arrival
+ * flags, k_ep.cu) -> every rank stores its int8 rows straight into the owners' receive buffers (peer stores over NVLink)
+ * -> rendezvous -> the owners run gate+up, SiLU+int8 and down on what they received, the down epilogue stores each
+ * result row straight into the token's rank -> rendezvous -> local combine, in the same order as on one GPU, so the
+ * hidden state is the same bits as without expert parallelism.  NCCL is used to form the group and for the benchmark's
+ * max-over-ranks; nothing on the data path calls it.
  * ================================================================================================================ */
 #include <dlfcn.h>
 #include <nccl.h>
@@ -677,9 +711,11 @@ static struct {
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
     const char *(*GetErrorString)(ncclResult_t);
+    int *xch; unsigned *epoch; unsigned long long timeout_ns;   /* exchange buffer (counts + arrival flags), rendezvous counter */
     int *all_cnt, *dst_base, *total, *nu_r, *ue_r, *ustart_r, *rx_qsum; float *rx_qs; int2 *rx_src; double *red;
-    void *peer[5][8];                       /* opened buffers of every rank: rx rows, rx scales, rx sums, rx return addresses, down rows */
-    void **peer_dev[5];                     /* the same tables in device memory */
+    void *peer[7][8];                       /* opened buffers of every rank: rx rows, rx scales, rx sums, rx return addresses, down rows, exchange, compact down rows */
+    void **peer_dev[7];
+    float *ds_all[GMOE_LAYERS]; const float **dsp[GMOE_LAYERS];   /* every expert's down scales gathered per layer, and the pointer table over them */                     /* the same tables in device memory */
 } EP;
 
 static int ep_nccl(const char *who) {
@@ -715,33 +751,61 @@ int gmoe_ep_init(int rank, int world, const void *id128) {
     EP_REALLOC(tiles_a, (R / 8 + NEXP) * sizeof(MoeTile)); EP_REALLOC(tiles_b, (R / 8 + NEXP) * sizeof(MoeTile));
     if (S.gu_dots) { EP_REALLOC(gu_dots, R * 2 * FFN * 4); EP_REALLOC(dn_dots, R * HID * 4); }
     if (tmap_bytes_2d("gmoe", &S.bmap_hq, S.hq_sorted, HID, R, HID, 128, UMMA_TN) || tmap_bytes_2d("gmoe", &S.bmap_aq, S.aq, FFN, R, FFN, 128, UMMA_TN)) return -1;
-    EP_ALLOC(all_cnt, (size_t)world * NEXP * 4); EP_ALLOC(dst_base, NEXP * 4); EP_ALLOC(total, 16); EP_ALLOC(nu_r, 16); EP_ALLOC(ue_r, NEXP * 4);
+    EP_ALLOC(xch, EP_XCH_INTS * 4); EP_ALLOC(epoch, 16); EP.all_cnt = EP.xch; EP.timeout_ns = 10000000000ull;
+    CU("gmoe", cudaMemset(EP.xch, 0, EP_XCH_INTS * 4)); CU("gmoe", cudaMemset(EP.epoch, 0, 16));
+    EP_ALLOC(dst_base, NEXP * 4); EP_ALLOC(total, 16); EP_ALLOC(nu_r, 16); EP_ALLOC(ue_r, NEXP * 4);
     EP_ALLOC(ustart_r, (NEXP + 1) * 4); EP_ALLOC(rx_qs, R * 4); EP_ALLOC(rx_qsum, R * 4); EP_ALLOC(rx_src, R * sizeof(int2)); EP_ALLOC(red, 64);
-    for (int k = 0; k < 5; k++) if (dmalloc((void **)&EP.peer_dev[k], 8 * sizeof(void *))) return fail("gmoe", "expert parallel: no device memory");
+    for (int k = 0; k < 7; k++) if (dmalloc((void **)&EP.peer_dev[k], 8 * sizeof(void *))) return fail("gmoe", "expert parallel: no device memory");
     S.ep_on = 1;
     return 0;
 }
-/* 5 x 64 bytes: the handles other ranks need to store into this rank's buffers */
-int gmoe_ep_handles(void *out320) {
+/* 7 x 64 bytes: the handles other ranks need to store into this rank's buffers */
+int gmoe_ep_handles(void *out448) {
     if (!S.ep_on) return fail("gmoe", "gmoe_ep_handles before gmoe_ep_init");
-    void *p[5] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down};
-    for (int k = 0; k < 5; k++) CU("gmoe", cudaIpcGetMemHandle((cudaIpcMemHandle_t *)((char *)out320 + 64 * k), p[k]));
+    void *p[7] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down, EP.xch, S.wire};
+    for (int k = 0; k < 7; k++) CU("gmoe", cudaIpcGetMemHandle((cudaIpcMemHandle_t *)((char *)out448 + 64 * k), p[k]));
     return 0;
 }
-/* all: world x 5 x 64 bytes, rank-major, as gathered from gmoe_ep_handles */
+/* all: world x 7 x 64 bytes, rank-major, as gathered from gmoe_ep_handles */
 int gmoe_ep_connect(const void *all) {
     if (!S.ep_on) return fail("gmoe", "gmoe_ep_connect before gmoe_ep_init");
-    void *mine[5] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down};
-    for (int r = 0; r < EP.world; r++) for (int k = 0; k < 5; k++) {
+    void *mine[7] = {S.hq_sorted, EP.rx_qs, EP.rx_qsum, EP.rx_src, S.down, EP.xch, S.wire};
+    for (int r = 0; r < EP.world; r++) for (int k = 0; k < 7; k++) {
         if (r == EP.rank) { EP.peer[k][r] = mine[k]; continue; }
-        cudaIpcMemHandle_t h; memcpy(&h, (const char *)all + ((size_t)r * 5 + k) * 64, 64);
+        cudaIpcMemHandle_t h; memcpy(&h, (const char *)all + ((size_t)r * 7 + k) * 64, 64);
         CU("gmoe", cudaIpcOpenMemHandle(&EP.peer[k][r], h, cudaIpcMemLazyEnablePeerAccess));
     }
-    for (int k = 0; k < 5; k++) CU("gmoe", cudaMemcpy(EP.peer_dev[k], EP.peer[k], 8 * sizeof(void *), cudaMemcpyHostToDevice));
+    for (int k = 0; k < 7; k++) CU("gmoe", cudaMemcpy(EP.peer_dev[k], EP.peer[k], 8 * sizeof(void *), cudaMemcpyHostToDevice));
     return 0;
 }
-static int ep_barrier(void) {   /* every rank's earlier work on its stream is complete before any rank's later work starts */
-    NC("gmoe", EP.AllReduce(EP.red, EP.red + 1, 1, ncclDouble, ncclSum, EP.comm, S.st)); return 0;
+/* every rank's earlier work on its stream is complete before any rank's later work starts; with cnt, every rank also receives
+ * every rank's pairs per expert */
+static int ep_barrier(const int *cnt) {
+    EpXchArgs a = {cnt, (int *const *)EP.peer_dev[5], EP.xch, EP.epoch, EP.rank, EP.world, EP.timeout_ns, S.err};
+    k_ep_exchange(S.st, &a); return 0;
+}
+/* The combine scales the compact down rows where the token lives, so every rank needs every expert's 2048 down scales: gathered
+ * once per layer (NCCL all-gather of 256/world x 8 KB per rank), the first time the layer runs in expert parallel.  Every rank
+ * runs the same layers, so the ranks make these calls together. */
+static int ep_layer_scales(int L) {
+    if (EP.dsp[L]) return 0;
+    LayerDev *l = &S.ly[L];
+    float *send = NULL;
+    if (dmalloc((void **)&EP.ds_all[L], (size_t)NEXP * HID * 4) || dmalloc((void **)&EP.dsp[L], NEXP * sizeof(void *)) || dmalloc((void **)&send, (size_t)EP.epr * HID * 4))
+        return fail("gmoe", "expert parallel: no device memory for the down scales of layer %d", L);
+    CU("gmoe", cudaMemcpyAsync(S.h_tab, l->tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyDeviceToHost, S.st));
+    CU("gmoe", cudaStreamSynchronize(S.st));
+    for (int k = 0; k < EP.epr; k++) {
+        const float *src = S.h_tab[EP.rank * EP.epr + k].ds;
+        if (!src) return fail("gmoe", "expert parallel: rank %d has no weights for its expert %d of layer %d", EP.rank, EP.rank * EP.epr + k, L);
+        CU("gmoe", cudaMemcpyAsync(send + (size_t)k * HID, src, HID * 4, cudaMemcpyDeviceToDevice, S.st));
+    }
+    NC("gmoe", EP.AllGather(send, EP.ds_all[L], (size_t)EP.epr * HID, ncclFloat, EP.comm, S.st));
+    for (int e = 0; e < NEXP; e++) S.h_dsp[e] = EP.ds_all[L] + (size_t)e * HID;
+    CU("gmoe", cudaMemcpyAsync(EP.dsp[L], S.h_dsp, NEXP * sizeof(void *), cudaMemcpyHostToDevice, S.st));
+    CU("gmoe", cudaStreamSynchronize(S.st));
+    cudaFree(send);
+    return 0;
 }
 static int run_layer_ep(int L, int nb, const float *bias) {
     LayerDev *l = &S.ly[L];
@@ -751,19 +815,19 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3);
     run_group(nb);
-    NC("gmoe", EP.AllGather(S.ecnt, EP.all_cnt, NEXP, ncclInt, EP.comm, S.st));
+    if (ep_barrier(S.ecnt)) return -1;
     EpPlanArgs p = {EP.all_cnt, EP.rank, EP.world, EP.dst_base, EP.nu_r, EP.ue_r, EP.ustart_r, EP.total, S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tn, UMMA_TN};
     k_ep_plan(S.st, &p);
     EpDispatchArgs d = {S.hq, S.hqs, S.hqsum, S.utok, S.uexp, S.estart, EP.dst_base, nb * TOPK, EP.rank, EP.epr,
                         (int8_t *const *)EP.peer_dev[0], (float *const *)EP.peer_dev[1], (int *const *)EP.peer_dev[2], (int2 *const *)EP.peer_dev[3]};
     k_ep_dispatch(S.st, &d);
-    if (ep_barrier()) return -1;
+    if (ep_barrier(NULL)) return -1;
     prof_end(3);
     ExpertArgs a; memset(&a, 0, sizeof a);
     a.tab = l->tab; a.maps = l->maps; a.ue = EP.ue_r; a.err = S.err; a.ptok = NULL;
     a.tiles = um ? S.tiles_b : S.tiles_a; a.ntiles = um ? S.ntiles_b : S.ntiles_a; a.max_tiles = (int)(EP.rcap / (um ? UMMA_TN : tn)) + NEXP;
     a.hq = S.hq_sorted; a.hqs = EP.rx_qs; a.hqsum = EP.rx_qsum; a.act = S.act; a.aq = S.aq; a.aqs = S.aqs; a.aqsum = S.aqsum; a.down = S.down;
-    a.rx_src = EP.rx_src; a.peer_down = (float *const *)EP.peer_dev[4];
+    a.rx_src = EP.rx_src; a.peer_down = (float *const *)EP.peer_dev[4]; a.peer_wire = (uint8_t *const *)EP.peer_dev[6]; a.wire = S.wire; a.wire_cap = S.maxp;
     if (S.keep || um) { a.gate = S.gate; a.up = S.up; }
     if (S.keep) { a.gu_dots = S.gu_dots; a.dn_dots = S.dn_dots; }
     prof_begin(4); if (um) k_gateup_umma(S.st, &a, &S.bmap_hq); else k_gateup_mma(S.st, &a, tn); prof_end(4);
@@ -773,8 +837,9 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     prof_end(5);
     prof_begin(6); if (um) k_down_umma(S.st, &a, &S.bmap_aq); else k_down_mma(S.st, &a, tn); prof_end(6);
     prof_begin(7);
-    if (ep_barrier()) return -1;
-    k_combine(S.st, S.down, S.uw, S.tp, S.x, S.x, nb);
+    if (ep_barrier(NULL)) return -1;
+    if (um && S.keep) k_wire_decode(S.st, S.wire, S.maxp, (const float *const *)EP.dsp[L], S.down, nb * TOPK);
+    run_combine((const float *const *)EP.dsp[L], nb, S.x, S.x);
     prof_end(7);
     return 0;
 }
@@ -782,7 +847,7 @@ static int run_layer_ep(int L, int nb, const float *bias) {
  * Device-resident form (gmoe_x_upload / gmoe_x_download, gmoe_chunks_upload); asynchronous; every rank calls it with the same nb. */
 int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
     if (!S.ep_on) return fail("gmoe", "expert parallelism is not set up");
-    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1;
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) return -1;
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     if (chunk >= 0) {
@@ -796,7 +861,7 @@ int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
 /* Host in/out, like gmoe_forward. */
 double gmoe_ep_forward(float *x, int nb, int l0, int nl, const float *bias) {
     if (!S.ep_on) { fail("gmoe", "expert parallelism is not set up"); return -1.0; }
-    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb)) return -1.0;
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) return -1.0;
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
@@ -813,6 +878,25 @@ int gmoe_ep_allmax(double *v) {
     NC("gmoe", EP.AllReduce(EP.red + 2, EP.red + 3, 1, ncclDouble, ncclMax, EP.comm, S.st));
     CU("gmoe", cudaMemcpyAsync(v, EP.red + 3, 8, cudaMemcpyDeviceToHost, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st)); return 0;
+}
+/* A rendezvous in which one of two arrivals never comes (no second rank exists): the wait must give up after `ms` milliseconds
+ * with the error code that the data path reports.  Returns that code (41), 0 if the wait returned without it, -1 on a CUDA error.
+ * Needs gmoe_init only. */
+int gmoe_ep_timeout_selftest(int ms) {
+    if (!S.ready) return fail("gmoe", "not initialised");
+    int *xch = NULL, **tab = NULL; unsigned *epoch = NULL; int code = -1;
+    if (dmalloc((void **)&xch, EP_XCH_INTS * 4) || dmalloc((void **)&tab, 8 * sizeof(void *)) || dmalloc((void **)&epoch, 16)) return fail("gmoe", "no device memory");
+    int *h_tab[8] = {xch, xch, 0, 0, 0, 0, 0, 0};
+    if (cudaMemset(xch, 0, EP_XCH_INTS * 4) == cudaSuccess && cudaMemset(epoch, 0, 16) == cudaSuccess &&
+        cudaMemcpy(tab, h_tab, sizeof h_tab, cudaMemcpyHostToDevice) == cudaSuccess) {
+        EpXchArgs a = {NULL, (int *const *)tab, xch, epoch, 0, 2, (unsigned long long)(ms > 0 ? ms : 1) * 1000000ull, S.err};
+        k_ep_exchange(S.st, &a);
+        if (cudaMemcpyAsync(S.h_err, S.err, 4, cudaMemcpyDeviceToHost, S.st) == cudaSuccess && cudaStreamSynchronize(S.st) == cudaSuccess) {
+            code = *S.h_err; *S.h_err = 0; cudaMemsetAsync(S.err, 0, 4, S.st); cudaStreamSynchronize(S.st);
+        }
+    }
+    cudaFree(xch); cudaFree(tab); cudaFree(epoch);
+    return code < 0 ? fail("gmoe", "rendezvous self-test: %s", cudaGetErrorString(cudaGetLastError())) : code;
 }
 /* received pairs of the last layer on this rank (load balance report) */
 int gmoe_ep_received(void) { int t = -1; if (S.ep_on) { cudaMemcpyAsync(&t, EP.total, 4, cudaMemcpyDeviceToHost, S.st); cudaStreamSynchronize(S.st); } return t; }

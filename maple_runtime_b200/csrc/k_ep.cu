@@ -2,7 +2,7 @@
 //
 // Rank r keeps tokens r*T .. (r+1)*T-1 and the experts r*E .. (r+1)*E-1 (E = 256 / world).  Its pairs are grouped by
 // global expert id (the same grouping as on one GPU), so the pairs for one destination rank are one contiguous run.
-// After an all-gather of the per-expert pair counts every rank can compute, without further communication, where each
+// After an exchange of the per-expert pair counts (peer stores plus arrival flags, ep_exchange_kernel) every rank can compute, without further communication, where each
 // of its pairs lands in the owner's receive buffer: the owner's pairs are ordered by (expert, source rank, source
 // order), i.e. global token order inside an expert.  The dispatch kernel then stores the int8 activation rows and their
 // scales straight into the owners' buffers over NVLink (plain peer stores, no multicast, no TMA on peer memory), and the
@@ -65,3 +65,38 @@ extern "C" void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d) {
     if (d->np <= 0) return;
     ep_dispatch_kernel<<<(d->np + 1) / 2, 256, 0, st>>>(*d); k_count_add(1);
 }
+
+// Rendezvous of the ranks, with the count exchange folded in.  One CTA per rank (each on its own GPU): thread e stores this
+// rank's count of expert e into every rank's table, the CTA fences, threads 0..world-1 then store this rank's arrival number
+// into every rank's flag line (release, system scope) and wait (acquire, bounded by the clock) until every rank's arrival number
+// has reached the same value in this rank's own lines.  Arrival numbers only grow, so a rank that is already one rendezvous
+// ahead still satisfies the wait.
+__device__ __forceinline__ unsigned long long ep_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__global__ void __launch_bounds__(NEXP) ep_exchange_kernel(EpXchArgs a) {
+    __shared__ unsigned s_epoch;
+    const int t = threadIdx.x;
+    if (t == 0) s_epoch = *a.epoch + 1u;
+    if (a.ecnt) {
+        const int c = a.ecnt[t];
+        for (int r = 0; r < a.world; r++) a.peer_xch[r][a.rank * NEXP + t] = c;
+    }
+    __threadfence_system();
+    __syncthreads();
+    const unsigned ep = s_epoch;
+    if (t < a.world) {
+        unsigned *dst = reinterpret_cast<unsigned *>(a.peer_xch[t] + EP_XCH_FLAGS) + a.rank * 16;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(ep) : "memory");
+        const unsigned *src = reinterpret_cast<const unsigned *>(a.xch + EP_XCH_FLAGS) + t * 16;
+        const unsigned long long t0 = ep_now_ns();
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            if ((int)(v - ep) >= 0) break;
+            if (ep_now_ns() - t0 > a.timeout_ns) { atomicExch(a.err, 41); break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    if (t == 0) *a.epoch = ep;
+}
+extern "C" void k_ep_exchange(cudaStream_t st, const EpXchArgs *a) { ep_exchange_kernel<<<1, NEXP, 0, st>>>(*a); k_count_add(1); }

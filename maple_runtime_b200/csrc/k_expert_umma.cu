@@ -2,7 +2,8 @@
 //
 // Work item = one tile (a used expert and up to 128 of its pairs) x one block of 2 x 128 weight rows:
 //   gate+up: 128 gate rows and the 128 up rows of the same index (the SiLU*up epilogue finds both in one thread);
-//   down:    two consecutive blocks of 128 down rows.
+//   down:    256 consecutive down rows, the even ones in accumulator 0 and the odd ones in accumulator 1 (a thread of the
+//            epilogue then holds two neighbouring rows and stores them as one word of the compact result row, kernels.h WIRE_*).
 // D[128 rows][N tokens] (s32, tensor memory) += A[128 rows][K] (u8 codes 0,1,2) x B[N tokens][K]^T (s8 activations).
 // A persistent grid (one CTA per SM) walks the items; every ring below keeps running across items, so the next item's
 // weights are already on their way while the current one is multiplied.
@@ -19,7 +20,8 @@
 //            tiled copies (box = 128 bytes x 128 rows, 128-byte swizzle = the K-major layout the MMA descriptor names).
 // A pipeline round is two 128-column blocks: the waits and commits of the MMA warps cost about as much as four MMAs each, so
 // they are paid once per eight MMAs.
-// Arithmetic = maple.c:425-458: out = (float)(sum(code*q) - qsum) * qs * s[r]; integer sums are exact.
+// Arithmetic = maple.c:425-458: out = (float)(sum(code*q) - qsum) * qs * s[r]; integer sums are exact.  gate+up scales here;
+// down stores sum(code*q) - qsum as integers and the combine applies qs and s[r] (same two roundings, same order).
 //
 // Warps (640 threads): 0-3 decode rows of accumulator 0, 4-7 rows of accumulator 1, 8 weight TMA, 9 B TMA, 10 and 11 MMA issue
 // (one warp per accumulator: a single thread cannot issue tcgen05.mma fast enough to fill the tensor pipe at N <= 80, two can),
@@ -153,8 +155,8 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                         tma_load_2d(dst, &em->gate, sb * 128, mb * 128, &sh->w_full[ws]);
                         tma_load_2d(dst + 128 * 128, &em->up, sb * 128, mb * 128, &sh->w_full[ws]);
                     } else {
-                        tma_load_2d(dst, &em->down, 0, mb * 256, &sh->w_full[ws]);
-                        tma_load_2d(dst + 128 * 128, &em->down, 0, mb * 256 + 128, &sh->w_full[ws]);
+                        tma_load_3d(dst, &em->down, 0, 0, mb * 128, &sh->w_full[ws]);             // the even rows of the 256-row block
+                        tma_load_3d(dst + 128 * 128, &em->down, 0, 1, mb * 128, &sh->w_full[ws]);   // the odd rows
                     }
                 }
             }
@@ -234,12 +236,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 #ifdef UMMA_TRACE
             long long tq0 = clock64();
 #endif
-            const int r0 = GATEUP ? mb * 128 + row : mb * 256 + row;
-            const float s0 = GATEUP ? ep.gs[r0] : ep.ds[r0], s1 = GATEUP ? ep.us[r0] : ep.ds[r0 + 128];
+            const int r0 = GATEUP ? mb * 128 + row : mb * 256 + 2 * row;      // down: accumulator 0 holds row r0, accumulator 1 row r0 + 1
+            const float s0 = GATEUP ? ep.gs[r0] : 0.0f, s1 = GATEUP ? ep.us[r0] : 0.0f;
             __syncwarp();
             for (int n = lane; n < N; n += 32) {
                 const int pair = tile.p0 + (n < cnt ? n : 0), t = (GATEUP && a.ptok) ? a.ptok[pair] : pair;
-                sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : a.aqsum[t];
+                sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : 32768 - a.aqsum[t];
             }
             __syncwarp();
 #ifdef UMMA_TRACE
@@ -265,24 +267,24 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->acc_empty);
                 }
-                float o0[16], o1[16];
-                {   // scale and code-sum correction of the piece's 16 tokens: eight 128-bit shared-memory reads
-                    const int4 *qsv = reinterpret_cast<const int4 *>(&sh->m_qsum[ew][c0]);
-                    const float4 *qfv = reinterpret_cast<const float4 *>(&sh->m_qs[ew][c0]);
-#pragma unroll
-                    for (int g4 = 0; g4 < 4; g4++) {
-                        const int4 qs4 = qsv[g4]; const float4 qf4 = qfv[g4];
-                        const int qsum[4] = {qs4.x, qs4.y, qs4.z, qs4.w}; const float qs[4] = {qf4.x, qf4.y, qf4.z, qf4.w};
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const int j = g4 * 4 + k, d0 = (int)v0[j] - qsum[k], d1 = (int)v1[j] - qsum[k];
-                            o0[j] = __fmul_rn(__fmul_rn((float)d0, qs[k]), s0); o1[j] = __fmul_rn(__fmul_rn((float)d1, qs[k]), s1);
-                            v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
-                        }
-                    }
-                }
                 const int lim = cnt - c0;                                 // tokens of this piece that exist
                 if (GATEUP) {
+                    float o0[16], o1[16];
+                    {   // scale and code-sum correction of the piece's 16 tokens: eight 128-bit shared-memory reads
+                        const int4 *qsv = reinterpret_cast<const int4 *>(&sh->m_qsum[ew][c0]);
+                        const float4 *qfv = reinterpret_cast<const float4 *>(&sh->m_qs[ew][c0]);
+#pragma unroll
+                        for (int g4 = 0; g4 < 4; g4++) {
+                            const int4 qs4 = qsv[g4]; const float4 qf4 = qfv[g4];
+                            const int qsum[4] = {qs4.x, qs4.y, qs4.z, qs4.w}; const float qs[4] = {qf4.x, qf4.y, qf4.z, qf4.w};
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j = g4 * 4 + k, d0 = (int)v0[j] - qsum[k], d1 = (int)v1[j] - qsum[k];
+                                o0[j] = __fmul_rn(__fmul_rn((float)d0, qs[k]), s0); o1[j] = __fmul_rn(__fmul_rn((float)d1, qs[k]), s1);
+                                v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
+                            }
+                        }
+                    }
                     // one base pointer per thread; the token index only adds a constant, so a store is one instruction
                     float *gp = a.gate + (size_t)(tile.p0 + c0) * 512 + r0, *up_ = a.up + (size_t)(tile.p0 + c0) * 512 + r0;
 #pragma unroll
@@ -292,23 +294,71 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll
                         for (int j = 0; j < 16; j++) if (j < lim) { dp[j * 1024] = (int)v0[j]; dp[j * 1024 + 512] = (int)v1[j]; }
                     }
-                } else if (!a.rx_src) {
-                    float *dp = a.down + (size_t)(tile.p0 + c0) * 2048 + r0;
+                } else {
+                    // compact rows: (dot + 32768) of this thread's two rows in one 32-bit word per token; the scales are applied where
+                    // the rows are combined.  Values that need more than 16 bits (|dot| >= 32768) take the escape plane below.
+                    uint32_t pk[16], wide = 0;
+                    {
+                        const int4 *qsv = reinterpret_cast<const int4 *>(&sh->m_qsum[ew][c0]);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) if (j < lim) { dp[j * 2048] = o0[j]; dp[j * 2048 + 128] = o1[j]; }
+                        for (int g4 = 0; g4 < 4; g4++) {
+                            const int4 qs4 = qsv[g4]; const int bq[4] = {qs4.x, qs4.y, qs4.z, qs4.w};       // 32768 - qsum
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j = g4 * 4 + k;
+                                v0[j] += (uint32_t)bq[k]; v1[j] += (uint32_t)bq[k];
+                                pk[j] = __byte_perm(v0[j], v1[j], 0x5410);
+                                wide |= v0[j] | v1[j];
+                            }
+                        }
+                    }
+                    const bool esc = __any_sync(0xffffffffu, (wide >> 16) != 0);
+                    const size_t rec0 = (size_t)a.wire_cap * WIRE_PITCH;            // the records sit behind the rows
+                    const bool recw = mb == 0 && q4 == 0 && lane < 16 && lane < lim; // one warp per piece writes the tokens' records
+                    if (!a.rx_src) {
+                        uint8_t *rowp = a.wire + (size_t)(tile.p0 + c0) * WIRE_PITCH;
+                        uint32_t *dp = reinterpret_cast<uint32_t *>(rowp) + (r0 >> 1);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (j < lim) dp[j * (WIRE_PITCH / 4)] = pk[j];
+                        if (recw) *reinterpret_cast<int2 *>(a.wire + rec0 + (size_t)(tile.p0 + c0 + lane) * WIRE_REC) = make_int2(__float_as_int(sh->m_qs[ew][c0 + lane]), tile.ex);
+                        if (esc) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) if (j < lim) {
+                                const uint32_t code = ((v0[j] >> 16) & 3u) | (((v1[j] >> 16) & 3u) << 2);
+                                if (code) {
+                                    atomicOr(reinterpret_cast<uint32_t *>(rowp + (size_t)j * WIRE_PITCH + 4096) + (r0 >> 4), code << ((r0 & 15) * 2));
+                                    atomicOr(reinterpret_cast<int *>(a.wire + rec0 + (size_t)(tile.p0 + c0 + j) * WIRE_REC + 8), 1 << (r0 >> 7));
+                                }
+                            }
+                        }
+                    } else {
+                        // expert parallel: each row goes to the rank that owns the token
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (j < lim) {
+                            const int2 sp = a.rx_src[tile.p0 + c0 + j];
+                            reinterpret_cast<uint32_t *>(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH)[r0 >> 1] = pk[j];
+                        }
+                        if (recw) {
+                            const int2 sp = a.rx_src[tile.p0 + c0 + lane];
+                            *reinterpret_cast<int2 *>(a.peer_wire[sp.x] + rec0 + (size_t)sp.y * WIRE_REC) = make_int2(__float_as_int(sh->m_qs[ew][c0 + lane]), tile.ex);
+                        }
+                        if (esc) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) if (j < lim) {
+                                const uint32_t code = ((v0[j] >> 16) & 3u) | (((v1[j] >> 16) & 3u) << 2);
+                                if (code) {
+                                    const int2 sp = a.rx_src[tile.p0 + c0 + j];
+                                    uint8_t *pb = a.peer_wire[sp.x];
+                                    atomicOr(reinterpret_cast<uint32_t *>(pb + (size_t)sp.y * WIRE_PITCH + 4096) + (r0 >> 4), code << ((r0 & 15) * 2));
+                                    atomicOr(reinterpret_cast<int *>(pb + rec0 + (size_t)sp.y * WIRE_REC + 8), 1 << (r0 >> 7));
+                                }
+                            }
+                        }
+                    }
                     if (a.dn_dots) {
                         int *ip = a.dn_dots + (size_t)(tile.p0 + c0) * 2048 + r0;
 #pragma unroll
-                        for (int j = 0; j < 16; j++) if (j < lim) { ip[j * 2048] = (int)v0[j]; ip[j * 2048 + 128] = (int)v1[j]; }
-                    }
-                } else {
-                    // expert parallel: each row goes to the rank that owns the token
-#pragma unroll
-                    for (int j = 0; j < 16; j++) if (j < lim) {
-                        const int2 sp = a.rx_src[tile.p0 + c0 + j];
-                        float *drow = a.peer_down[sp.x] + (size_t)sp.y * 2048 + r0;
-                        drow[0] = o0[j]; drow[128] = o1[j];
-                        if (a.dn_dots) { a.dn_dots[(size_t)(tile.p0 + c0 + j) * 2048 + r0] = (int)v0[j]; a.dn_dots[(size_t)(tile.p0 + c0 + j) * 2048 + r0 + 128] = (int)v1[j]; }
+                        for (int j = 0; j < 16; j++) if (j < lim) *reinterpret_cast<int2 *>(ip + j * 2048) = make_int2((int)v0[j] - 32768, (int)v1[j] - 32768);
                     }
                 }
 #ifdef UMMA_TRACE

@@ -35,6 +35,9 @@ typedef struct {
     float *gate, *up; int32_t *gu_dots, *dn_dots;
     /* expert parallel: the down rows go to the rank that owns the token: rx_src[pair] = (rank, pair slot there), peer_down[rank] = its [pairs][2048] buffer */
     const int2 *rx_src; float *const *peer_down;
+    /* the tcgen05 down kernel stores compact rows (see WIRE_* below) instead of fp32 ones: wire [np] rows, or in expert parallel
+     * peer_wire[rank] = that rank's buffer */
+    uint8_t *wire; uint8_t *const *peer_wire; int wire_cap;   /* wire_cap: pairs each such buffer is laid out for */
     int *err;                /* set to 1 by a kernel whose bounded wait ran out */
 } ExpertArgs;
 
@@ -73,6 +76,24 @@ void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
 
+/* ---- compact down rows (the tcgen05 path) ----
+ * The down projection's results leave the expert kernel as integers and are scaled where they are combined: half the bytes of
+ * fp32 rows through HBM and, in expert parallel, over NVLink.  A row of a pair is WIRE_PITCH bytes:
+ *   [0, 4096)     2048 x uint16: the low 16 bits of (dot + 32768), dot = sum(code*q) - qsum in -65024..65024;
+ *   [4096, 4608)  2048 x 2 bits (row r: word r/16, bits 2(r%16)..): bits 16-17 of (dot + 32768), written (OR-ed in) only when a
+ *                 value does not fit 16 bits; zero otherwise and cleared again by the kernel that consumes them.
+ * Behind the rows of a buffer of np_cap pairs sit np_cap records {float scale of the pair's int8 row; int index of the expert
+ * in the table of down-scale pointers; int has-escapes flag; int unused}. */
+#define WIRE_PITCH 4608
+#define WIRE_REC 16
+#define WIRE_BYTES(np_cap) ((size_t)(np_cap) * (WIRE_PITCH + WIRE_REC))
+/* out[b] = init[b] (or 0) + sum over the token's pairs, in the order of tp, of uw * ((float)dot * scale * ds[expert][row]): the
+ * same operations in the same order as the fp32 form (k_combine after a down kernel that scaled).  dsp[ex] = 2048 down scales. */
+void k_combine_wire(cudaStream_t st, uint8_t *wire, int np_cap, const float *const *dsp, const float *uw, const int *tp,
+                    const float *init, float *out, int nb);
+/* fp32 rows [np][2048] from compact ones (stage comparisons); leaves the escape planes as they are */
+void k_wire_decode(cudaStream_t st, const uint8_t *wire, int np_cap, const float *const *dsp, float *down, int np);
+
 /* ---- expert parallel (k_ep.cu) ---- */
 typedef struct {
     const int *all_cnt;      /* [world][256] pairs per expert of every rank */
@@ -89,6 +110,20 @@ typedef struct {
     int8_t *const *peer_hq; float *const *peer_qs; int *const *peer_qsum; int2 *const *peer_src;   /* [world] receive buffers */
 } EpDispatchArgs;
 void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d);
+/* Exchange buffer of a rank, written by its peers: int counts[8][256] (pairs per expert of every rank), then one 64-byte line per
+ * source rank whose first word is that rank's arrival number. */
+#define EP_XCH_FLAGS (8 * 256)
+#define EP_XCH_INTS (EP_XCH_FLAGS + 8 * 16)
+typedef struct {
+    const int *ecnt;           /* this rank's [256] pairs per expert, stored into every rank's counts[rank]; NULL: rendezvous only */
+    int *const *peer_xch;      /* [world] exchange buffers, this rank's own among them */
+    int *xch;                  /* this rank's own */
+    unsigned *epoch;           /* [1] device counter: rendezvous made so far (every rank makes the same sequence) */
+    int rank, world; unsigned long long timeout_ns; int *err;
+} EpXchArgs;
+/* All ranks meet: everything a rank's stream did before is complete and visible before any rank's later work starts.  A wait
+ * that lasts longer than timeout_ns stores 41 into *err and returns. */
+void k_ep_exchange(cudaStream_t st, const EpXchArgs *a);
 
 void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
 

@@ -126,6 +126,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void *tmap,
                  ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
+// the 3-D form: x = innermost coordinate (same alignment rule), y, z = the outer two
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void *tmap, int x, int y, int z, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---- asynchronous 16-byte copies global -> shared (gathered activation rows) -------------------------------------
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");

@@ -35,7 +35,7 @@ def setup(g, rank, world, all_gather):
         g._chk(lib.gmoe_ep_unique_id(uid))
     uid_raw = all_gather(uid.raw)[0]
     g._chk(lib.gmoe_ep_init(rank, world, uid_raw))
-    h = C.create_string_buffer(320)
+    h = C.create_string_buffer(448)
     g._chk(lib.gmoe_ep_handles(h))
     allh = b"".join(all_gather(h.raw))
     g._chk(lib.gmoe_ep_connect(allh))

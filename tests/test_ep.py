@@ -48,3 +48,15 @@ def test_two_gpus_equal_single_gpu_oracle(nb, layers, zipf):
     r = run_ranks(2, "gpu", nb, layers, zipf)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("equal bits True") == 4
+
+
+@pytest.mark.gpu
+def test_rendezvous_gives_up_when_a_rank_never_arrives(gpu):
+    """Failure detection of the expert-parallel rendezvous without a GPU fault: a wait on an arrival flag that nothing sets
+    ends after its limit with the status the host reads; the context stays usable."""
+    import time
+    t0 = time.perf_counter()
+    assert gpu.lib.gmoe_ep_timeout_selftest(200) == 41
+    dt = time.perf_counter() - t0
+    assert 0.15 < dt < 5.0
+    assert gpu.lib.gmoe_ep_timeout_selftest(20) == 41        # and again: the first give-up left nothing behind

@@ -101,6 +101,52 @@ def test_tiled_router_equals_oracle_for_every_tile_size(nb, tt, layers, clib, or
         clib.k_router_tile_force(0)
 
 
+def test_compact_down_rows_escape_plane(layers, clib, oracle, weights):
+    """The tcgen05 down kernel stores dot + 32768 in 16 bits and the rare |dot| >= 32768 through a 2-bit escape plane.  Down rows
+    of all +1 / all -1 against int8 rows of all +-127 give dots of +-65024: both signs of the escape, next to ordinary values;
+    the result must equal the register-decode path's and the expected integers, and the plane must be clean afterwards."""
+    from maple_runtime_b200 import lib as ml
+    g = layers
+    router, post_ln, experts = weights.layer(2)
+    ex = experts.copy().reshape(256, ml.CONST.EXPERT_BYTES)
+    dn = ex[:, 2 * ml.CONST.GU_BYTES:2 * ml.CONST.GU_BYTES + ml.CONST.GU_CODES].reshape(256, 2048, 128)
+    dn[:, 0:300, :] = 0xAA        # code 2 everywhere: t = +1
+    dn[:, 300:640, :] = 0x00      # code 0 everywhere: t = -1
+    dn[:, 1500:1503, :] = 0xAA
+    span = ml.page_aligned(ex.nbytes)
+    span[:ex.nbytes] = ex.reshape(-1)
+    rid = g.region(span)
+    g.set_layer(3, router, post_ln, ml.gloc_for_contiguous(0, slot=0), np.array([rid, -1, -1, -1], np.int32))
+    nb = 600
+    x = weights.hidden(311, nb)
+    g.poke("x", x)
+    g.set_path(2)
+    try:
+        for st in ("norm", "router", "topk", "group", "gateup", "actq"):
+            g.stage(st, 3, nb)
+        aq = g.peek("aq", nb).copy()
+        aq[0::3] = 127; aq[1::3] = -127                                   # every third pair keeps its ordinary row
+        g.poke("aq", aq); g.poke("aqsum", aq.astype(np.int32).sum(1).astype(np.int32))
+        g.stage("down", 3, nb); g.stage("combine_y", 3, nb)
+        dots2, down2, y2 = g.peek("dn_dots", nb).copy(), g.peek("down", nb).copy(), g.peek("y", nb).copy()
+        g.set_path(1)
+        g.stage("down", 3, nb); g.stage("combine_y", 3, nb)
+        dots1, down1, y1 = g.peek("dn_dots", nb), g.peek("down", nb), g.peek("y", nb)
+        assert dots2.max() == 65024 and dots2.min() == -65024
+        assert np.array_equal(dots2, dots1)
+        assert same_bits(down2, down1) and same_bits(y2, y1)
+        ustart = g.peek("ustart", nb)
+        rows = aq[ustart[0]:ustart[1]].astype(np.int64)                    # first used expert: the expected integers of uniform rows
+        assert np.array_equal(dots2[ustart[0]:ustart[1]][:, [0, 299, 300, 639, 1501]], np.stack([rows.sum(1), rows.sum(1), -rows.sum(1), -rows.sum(1), rows.sum(1)], 1))
+        # the escapes were consumed: an ordinary pass through the same layer equals the oracle again
+        g.set_path(2)
+        want, _ = oracle.moe(router, post_ln, ex.reshape(-1), x, 1)
+        got = x.copy(); g.forward(got, 3, 1)
+        assert same_bits(got, want)
+    finally:
+        g.set_path(0)
+
+
 @pytest.mark.parametrize("case", list(mg.CASES))
 def test_fixtures_from_the_reference(case, layers, clib):
     """The reference's own outputs (tests/golden) without the oracle in between."""
