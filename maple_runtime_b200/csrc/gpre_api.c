@@ -400,40 +400,48 @@ static double finish(const char *who) {
  * Every kernel takes its sizes from device memory, so the sequence for (nb, l0, nl, bias?, path) is the same every time and can
  * be replayed.  The second call with a key captures it (the first runs plainly, so that one-time set-up calls made by the
  * launchers happen outside a capture).  Per-stage events are captured as event-record nodes, so gmoe_profile_read then reports the
- * last replay.  Not used while stages are kept, under expert parallelism, or when GMOE_GRAPH=0 is set. */
+ * last replay.  Not used while stages are kept or when GMOE_GRAPH=0 is set.  Under expert parallelism the ranks make the same calls
+ * in the same order, so they capture and replay together; nothing on that path calls NCCL. */
 #define NGRAPH 16
-static struct { int nb, l0, nl, bias, path, prof, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
+static struct { int nb, l0, nl, bias, path, prof, ep, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
 static int g_graph_on = -1;
 static int graphs_on(void) {
     if (g_graph_on < 0) { const char *e = getenv("GMOE_GRAPH"); g_graph_on = !(e && e[0] == '0'); }
-    return g_graph_on && !S.keep && !S.ep_on;
+    return g_graph_on && !S.keep;
 }
 int gmoe_set_graph(int on) { g_graph_on = on != 0; return 0; }
-static int layers_enqueue(int nb, int l0, int nl, const float *bd) {
-    if (!graphs_on()) { for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd); return 0; }
+static int run_layer_ep(int L, int nb, const float *bias);
+static int layers_run(int nb, int l0, int nl, const float *bd, int ep) {
+    for (int L = l0; L < l0 + nl; L++) { if (ep) { if (run_layer_ep(L, nb, bd)) return -1; } else run_layer(L, nb, 1, bd); }
+    return 0;
+}
+static int layers_enqueue_ep(int nb, int l0, int nl, const float *bd, int ep) {
+    if (!graphs_on()) return layers_run(nb, l0, nl, bd, ep);
     int k = -1, free_k = -1;
     for (int i = 0; i < NGRAPH; i++) {
-        if (GR[i].seen && GR[i].nb == nb && GR[i].l0 == l0 && GR[i].nl == nl && GR[i].bias == (bd != NULL) && GR[i].path == S.path && GR[i].prof == (int)S.prof_mask) { k = i; break; }
+        if (GR[i].seen && GR[i].nb == nb && GR[i].l0 == l0 && GR[i].nl == nl && GR[i].bias == (bd != NULL) && GR[i].path == S.path && GR[i].prof == (int)S.prof_mask && GR[i].ep == ep) { k = i; break; }
         if (!GR[i].seen && free_k < 0) free_k = i;
     }
     if (k < 0) {   /* first sight: run plainly and remember the key */
-        for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
-        if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path; GR[free_k].prof = (int)S.prof_mask; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
+        if (layers_run(nb, l0, nl, bd, ep)) return -1;
+        if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path; GR[free_k].prof = (int)S.prof_mask; GR[free_k].ep = ep; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
         return 0;
     }
     if (!GR[k].exec) {
         cudaGraph_t g = NULL; long before = k_count();
-        if (cudaStreamBeginCapture(S.st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd); return 0; }
-        for (int L = l0; L < l0 + nl; L++) run_layer(L, nb, 1, bd);
+        if (cudaStreamBeginCapture(S.st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return layers_run(nb, l0, nl, bd, ep);
+        int bad = layers_run(nb, l0, nl, bd, ep);
         cudaError_t e = cudaStreamEndCapture(S.st, &g);
         GR[k].launches = k_count() - before;
-        if (e == cudaSuccess) e = cudaGraphInstantiate(&GR[k].exec, g, 0);
+        if (e == cudaSuccess && !bad) e = cudaGraphInstantiate(&GR[k].exec, g, 0);
         if (g) cudaGraphDestroy(g);
+        if (bad) { GR[k].exec = NULL; GR[k].seen = 2; return -1; }
         if (e != cudaSuccess) { GR[k].exec = NULL; GR[k].seen = 2; cudaGetLastError(); return fail("gmoe", "graph capture of the layer loop: %s", cudaGetErrorString(e)); }
     } else k_count_add(GR[k].launches);
     CU("gmoe", cudaGraphLaunch(GR[k].exec, S.st));
     return 0;
 }
+static int layers_enqueue(int nb, int l0, int nl, const float *bd) { return layers_enqueue_ep(nb, l0, nl, bd, 0); }
 
 double gmoe_moe(int L, const float *x, int nb, float *y, const float *bias) {
     if (check_call("gmoe", L, nb)) return -1.0;
@@ -854,7 +862,7 @@ int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
         if (!S.ring || nb != S.ring_nb || chunk >= S.ring_n) return fail("gmoe", "chunk %d of %d tokens is not in the ring", chunk, nb);
         cudaMemcpyAsync(S.x, S.ring + (size_t)chunk * nb * HID, (size_t)nb * HID * 4, cudaMemcpyDeviceToDevice, S.st);
     }
-    for (int L = l0; L < l0 + nl; L++) if (run_layer_ep(L, nb, bd)) return -1;
+    if (layers_enqueue_ep(nb, l0, nl, bd, 1)) return -1;
     cudaEventRecord(S.e1, S.st);
     S.nb_cur = nb; return 0;
 }
@@ -865,7 +873,7 @@ double gmoe_ep_forward(float *x, int nb, int l0, int nl, const float *bias) {
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
-    for (int L = l0; L < l0 + nl; L++) if (run_layer_ep(L, nb, bd)) return -1.0;
+    if (layers_enqueue_ep(nb, l0, nl, bd, 1)) return -1.0;
     CUD("gmoe", cudaMemcpyAsync(x, S.x, (size_t)nb * HID * 4, cudaMemcpyDeviceToHost, S.st));
     cudaEventRecord(S.e1, S.st);
     S.nb_cur = nb;

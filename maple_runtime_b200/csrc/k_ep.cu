@@ -21,12 +21,19 @@ __global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p) {
     const int epr = NEXP / p.world, owner = e / epr, mine = owner == p.rank;
     int tot = 0, before = 0;
     for (int s = 0; s < p.world; s++) { int c = p.all_cnt[s * NEXP + e]; if (s < p.rank) before += c; tot += c; }
-    s_tot[e] = tot;
+    // offset of expert e inside its owner's buffer: the totals of the owner's earlier experts (a prefix sum over all experts,
+    // taken relative to the owner's first expert)
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+    if (lane == 31) w_sum[wid][0] = incl;
     __syncthreads();
-    // offset of expert e inside its owner's buffer: the totals of the owner's earlier experts
-    int base = 0;
-    for (int k = owner * epr; k < e; k++) base += s_tot[k];
-    p.dst_base[e] = base + before;
+    int woff = 0;
+    for (int w = 0; w < wid; w++) woff += w_sum[w][0];
+    s_tot[e] = woff + incl - tot;                  // exclusive prefix
+    __syncthreads();
+    p.dst_base[e] = s_tot[e] - s_tot[owner * epr] + before;
+    __syncthreads();                               // w_sum is reused below
     // the owner's own view: only its experts count below
     const int cnt = mine ? tot : 0, used = cnt > 0;
     const int na = (cnt + p.tn_a - 1) / p.tn_a, nb = (cnt + p.tn_b - 1) / p.tn_b;
@@ -67,7 +74,7 @@ extern "C" void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d) {
 }
 
 // Rendezvous of the ranks, with the count exchange folded in.  One CTA per rank (each on its own GPU): thread e stores this
-// rank's count of expert e into every rank's table, the CTA fences, threads 0..world-1 then store this rank's arrival number
+// rank's count of expert e into every rank's table, after a CTA barrier threads 0..world-1 store this rank's arrival number
 // into every rank's flag line (release, system scope) and wait (acquire, bounded by the clock) until every rank's arrival number
 // has reached the same value in this rank's own lines.  Arrival numbers only grow, so a rank that is already one rendezvous
 // ahead still satisfies the wait.
@@ -80,8 +87,7 @@ __global__ void __launch_bounds__(NEXP) ep_exchange_kernel(EpXchArgs a) {
         const int c = a.ecnt[t];
         for (int r = 0; r < a.world; r++) a.peer_xch[r][a.rank * NEXP + t] = c;
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();                                     // the release stores below order the CTA's count stores before the flags
     const unsigned ep = s_epoch;
     if (t < a.world) {
         unsigned *dst = reinterpret_cast<unsigned *>(a.peer_xch[t] + EP_XCH_FLAGS) + a.rank * 16;

@@ -53,6 +53,7 @@ struct __align__(16) UmShared {
     uint32_t tmem_base; int abort_flag;
     unsigned long long exp_tab[32];
     __align__(16) float m_qs[8][UM_TN]; __align__(16) int m_qsum[8][UM_TN];      // per epilogue warp: scale and code-sum correction of the tile's tokens
+    __align__(16) unsigned long long m_dst[8][UM_TN];                             // expert parallel, down: where each token's compact row lives (a peer's memory)
 };
 
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
@@ -242,6 +243,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             for (int n = lane; n < N; n += 32) {
                 const int pair = tile.p0 + (n < cnt ? n : 0), t = (GATEUP && a.ptok) ? a.ptok[pair] : pair;
                 sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : 32768 - a.aqsum[t];
+                if (!GATEUP && a.rx_src) { const int2 sp = a.rx_src[pair]; sh->m_dst[ew][n] = (unsigned long long)(uintptr_t)(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH); }
             }
             __syncwarp();
 #ifdef UMMA_TRACE
@@ -333,10 +335,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                         }
                     } else {
                         // expert parallel: each row goes to the rank that owns the token
+                        const ulonglong2 *dv = reinterpret_cast<const ulonglong2 *>(&sh->m_dst[ew][c0]);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) if (j < lim) {
-                            const int2 sp = a.rx_src[tile.p0 + c0 + j];
-                            reinterpret_cast<uint32_t *>(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH)[r0 >> 1] = pk[j];
+                        for (int j2 = 0; j2 < 8; j2++) {
+                            const ulonglong2 d2 = dv[j2];
+                            if (2 * j2 < lim) reinterpret_cast<uint32_t *>((uintptr_t)d2.x)[r0 >> 1] = pk[2 * j2];
+                            if (2 * j2 + 1 < lim) reinterpret_cast<uint32_t *>((uintptr_t)d2.y)[r0 >> 1] = pk[2 * j2 + 1];
                         }
                         if (recw) {
                             const int2 sp = a.rx_src[tile.p0 + c0 + lane];
