@@ -54,7 +54,7 @@ static struct {
     unsigned *mask; int *err, *h_err;
     MoeTile *tiles_a, *tiles_b;
     ExpertPtrs *tab_call;      /* the used experts of one gpre_moe call */
-    ExpertMaps *maps_call, *h_maps; int8_t *hq_sorted; TMap bmap_hq, bmap_aq;
+    ExpertMaps *maps_call, *h_maps; int8_t *hq_sorted; TMap4 bmap_hq, bmap_aq;
     struct { const void *key; ExpertMaps m; } *map_cache;   /* tensor maps of experts seen by gpre_moe, by code pointer */
     MoeTile *h_tiles; ExpertPtrs *h_tab;   /* host staging for the reference-shaped calls */
     double t_experts;          /* GPU seconds in gfull_moe, reported by gfull_report */
@@ -104,6 +104,8 @@ static int expert_maps(const char *who, const ExpertPtrs *e, ExpertMaps *m) {
     return 0;
 }
 
+/* the B operands of the tcgen05 kernels (int8 rows in pair order), one map per box height 32, 64, 96, 128 */
+static int bmaps(const char *who, size_t pairs);
 static int init_common(const char *who, int maxtok, int topk) {
     if (topk != TOPK) return fail(who, "topk %d is not supported (the kernels are built for %d)", topk, TOPK);
     if (maxtok < 1 || maxtok > GMOE_MAXTOK_LIMIT) return fail(who, "maxtok %d outside 1..%d", maxtok, GMOE_MAXTOK_LIMIT);
@@ -130,7 +132,7 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16); ALLOC(maps_call, NEXP * sizeof(ExpertMaps)); ALLOC(hq_sorted, P * HID);
     ALLOC(wire, WIRE_BYTES(P)); CU(who, cudaMemset(S.wire, 0, WIRE_BYTES(P))); ALLOC(dsp_call, NEXP * sizeof(void *));
     if (tmap_init(who)) return -1;
-    if (tmap_bytes_2d(who, &S.bmap_hq, S.hq_sorted, HID, P, HID, 128, UMMA_TN) || tmap_bytes_2d(who, &S.bmap_aq, S.aq, FFN, P, FFN, 128, UMMA_TN)) return -1;
+    if (bmaps(who, P)) return -1;
     CU(who, cudaMemset(S.err, 0, 16));
     CU(who, cudaHostAlloc((void **)&S.h_err, 16, cudaHostAllocDefault)); *S.h_err = 0;
     S.h_tiles = malloc(2 * (P / 8 + NEXP) * sizeof(MoeTile)); S.h_tab = malloc(NEXP * sizeof(ExpertPtrs));
@@ -140,6 +142,12 @@ static int init_common(const char *who, int maxtok, int topk) {
     S.ready = 1;
     fprintf(stderr, "%s: %s, chunks up to %d tokens, %.0f MB of device workspace, weights resident in HBM\n", who, pr.name, maxtok,
             (double)(T * HID * 13 + P * (FFN * 5 + HID * 4 + 40)) / 1e6);
+    return 0;
+}
+static int bmaps(const char *who, size_t pairs) {
+    for (int i = 0; i < 4; i++)
+        if (tmap_bytes_2d(who, &S.bmap_hq.m[i], S.hq_sorted, HID, pairs, HID, 128, 32 * (i + 1)) ||
+            tmap_bytes_2d(who, &S.bmap_aq.m[i], S.aq, FFN, pairs, FFN, 128, 32 * (i + 1))) return -1;
     return 0;
 }
 int gpre_init(int maxtok, int topk) { return init_common("gpre", maxtok, topk); }
@@ -758,7 +766,7 @@ int gmoe_ep_init(int rank, int world, const void *id128) {
     EP_REALLOC(aq, R * FFN); EP_REALLOC(aqs, R * 4); EP_REALLOC(aqsum, R * 4);
     EP_REALLOC(tiles_a, (R / 8 + NEXP) * sizeof(MoeTile)); EP_REALLOC(tiles_b, (R / 8 + NEXP) * sizeof(MoeTile));
     if (S.gu_dots) { EP_REALLOC(gu_dots, R * 2 * FFN * 4); EP_REALLOC(dn_dots, R * HID * 4); }
-    if (tmap_bytes_2d("gmoe", &S.bmap_hq, S.hq_sorted, HID, R, HID, 128, UMMA_TN) || tmap_bytes_2d("gmoe", &S.bmap_aq, S.aq, FFN, R, FFN, 128, UMMA_TN)) return -1;
+    if (bmaps("gmoe", R)) return -1;
     EP_ALLOC(xch, EP_XCH_INTS * 4); EP_ALLOC(epoch, 16); EP.all_cnt = EP.xch; EP.timeout_ns = 10000000000ull;
     CU("gmoe", cudaMemset(EP.xch, 0, EP_XCH_INTS * 4)); CU("gmoe", cudaMemset(EP.epoch, 0, 16));
     EP_ALLOC(dst_base, NEXP * 4); EP_ALLOC(total, 16); EP_ALLOC(nu_r, 16); EP_ALLOC(ue_r, NEXP * 4);
@@ -823,9 +831,9 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3);
     run_group(nb);
-    if (ep_barrier(S.ecnt)) return -1;
     EpPlanArgs p = {EP.all_cnt, EP.rank, EP.world, EP.dst_base, EP.nu_r, EP.ue_r, EP.ustart_r, EP.total, S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tn, UMMA_TN};
-    k_ep_plan(S.st, &p);
+    EpXchArgs xc = {S.ecnt, (int *const *)EP.peer_dev[5], EP.xch, EP.epoch, EP.rank, EP.world, EP.timeout_ns, S.err};
+    k_ep_plan(S.st, &p, &xc);
     EpDispatchArgs d = {S.hq, S.hqs, S.hqsum, S.utok, S.uexp, S.estart, EP.dst_base, nb * TOPK, EP.rank, EP.epr,
                         (int8_t *const *)EP.peer_dev[0], (float *const *)EP.peer_dev[1], (int *const *)EP.peer_dev[2], (int2 *const *)EP.peer_dev[3]};
     k_ep_dispatch(S.st, &d);

@@ -14,9 +14,44 @@
 extern "C" void k_count_add(long n);
 #define NEXP 256
 
+// Rendezvous of the ranks, with the count exchange folded in.  One CTA per rank (each on its own GPU): thread e stores this
+// rank's count of expert e into every rank's table, after a CTA barrier threads 0..world-1 store this rank's arrival number
+// into every rank's flag line (release, system scope) and wait (acquire, bounded by the clock) until every rank's arrival number
+// has reached the same value in this rank's own lines.  Arrival numbers only grow, so a rank that is already one rendezvous
+// ahead still satisfies the wait.
+__device__ __forceinline__ unsigned long long ep_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void ep_rendezvous(const EpXchArgs &a) {
+    __shared__ unsigned s_epoch;
+    const int t = threadIdx.x;
+    if (t == 0) s_epoch = *a.epoch + 1u;
+    if (a.ecnt) {
+        const int c = a.ecnt[t];
+        for (int r = 0; r < a.world; r++) a.peer_xch[r][a.rank * NEXP + t] = c;
+    }
+    __syncthreads();                                     // the release stores below order the CTA's count stores before the flags
+    const unsigned ep = s_epoch;
+    if (t < a.world) {
+        unsigned *dst = reinterpret_cast<unsigned *>(a.peer_xch[t] + EP_XCH_FLAGS) + a.rank * 16;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(ep) : "memory");
+        const unsigned *src = reinterpret_cast<const unsigned *>(a.xch + EP_XCH_FLAGS) + t * 16;
+        const unsigned long long t0 = ep_now_ns();
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            if ((int)(v - ep) >= 0) break;
+            if (ep_now_ns() - t0 > a.timeout_ns) { atomicExch(a.err, 41); break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    if (t == 0) *a.epoch = ep;
+}
+__global__ void __launch_bounds__(NEXP) ep_exchange_kernel(EpXchArgs a) { ep_rendezvous(a); }
+
 // one CTA, thread e = global expert
-__global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p) {
+__global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p, EpXchArgs xc) {
     __shared__ int s_tot[NEXP], w_sum[8][4];
+    if (xc.peer_xch) ep_rendezvous(xc);            // the count exchange first: every rank's counts are in all_cnt after it
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
     const int epr = NEXP / p.world, owner = e / epr, mine = owner == p.rank;
     int tot = 0, before = 0;
@@ -57,7 +92,9 @@ __global__ void __launch_bounds__(NEXP) ep_plan_kernel(EpPlanArgs p) {
         *p.nu = nu; p.ustart[nu] = start + cnt; *p.total = start + cnt; *p.ntiles_a = ta0 + na; *p.ntiles_b = tb0 + nb;
     }
 }
-extern "C" void k_ep_plan(cudaStream_t st, const EpPlanArgs *p) { ep_plan_kernel<<<1, NEXP, 0, st>>>(*p); k_count_add(1); }
+extern "C" void k_ep_plan(cudaStream_t st, const EpPlanArgs *p, const EpXchArgs *x) {
+    EpXchArgs none = {0}; ep_plan_kernel<<<1, NEXP, 0, st>>>(*p, x ? *x : none); k_count_add(1);
+}
 
 // 128 threads per pair: the 2048-byte int8 row and its scale, code-sum correction and return address to the owner
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpDispatchArgs d) {
@@ -73,36 +110,4 @@ extern "C" void k_ep_dispatch(cudaStream_t st, const EpDispatchArgs *d) {
     ep_dispatch_kernel<<<(d->np + 1) / 2, 256, 0, st>>>(*d); k_count_add(1);
 }
 
-// Rendezvous of the ranks, with the count exchange folded in.  One CTA per rank (each on its own GPU): thread e stores this
-// rank's count of expert e into every rank's table, after a CTA barrier threads 0..world-1 store this rank's arrival number
-// into every rank's flag line (release, system scope) and wait (acquire, bounded by the clock) until every rank's arrival number
-// has reached the same value in this rank's own lines.  Arrival numbers only grow, so a rank that is already one rendezvous
-// ahead still satisfies the wait.
-__device__ __forceinline__ unsigned long long ep_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-__global__ void __launch_bounds__(NEXP) ep_exchange_kernel(EpXchArgs a) {
-    __shared__ unsigned s_epoch;
-    const int t = threadIdx.x;
-    if (t == 0) s_epoch = *a.epoch + 1u;
-    if (a.ecnt) {
-        const int c = a.ecnt[t];
-        for (int r = 0; r < a.world; r++) a.peer_xch[r][a.rank * NEXP + t] = c;
-    }
-    __syncthreads();                                     // the release stores below order the CTA's count stores before the flags
-    const unsigned ep = s_epoch;
-    if (t < a.world) {
-        unsigned *dst = reinterpret_cast<unsigned *>(a.peer_xch[t] + EP_XCH_FLAGS) + a.rank * 16;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(ep) : "memory");
-        const unsigned *src = reinterpret_cast<const unsigned *>(a.xch + EP_XCH_FLAGS) + t * 16;
-        const unsigned long long t0 = ep_now_ns();
-        for (;;) {
-            unsigned v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
-            if ((int)(v - ep) >= 0) break;
-            if (ep_now_ns() - t0 > a.timeout_ns) { atomicExch(a.err, 41); break; }
-            __nanosleep(64);
-        }
-    }
-    __syncthreads();
-    if (t == 0) *a.epoch = ep;
-}
 extern "C" void k_ep_exchange(cudaStream_t st, const EpXchArgs *a) { ep_exchange_kernel<<<1, NEXP, 0, st>>>(*a); k_count_add(1); }

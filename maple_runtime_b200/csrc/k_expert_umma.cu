@@ -17,7 +17,8 @@
 //            order; convert.py:29-33) and writes the block with tcgen05.st into the tensor-memory A operand: lane = row,
 //            one 32-bit cell = four consecutive K values.  Decoded weights never touch shared memory;
 //   B        int8 activation rows in pair order (a gather kernel puts the tokens' rows into expert-grouped order first), TMA
-//            tiled copies (box = 128 bytes x 128 rows, 128-byte swizzle = the K-major layout the MMA descriptor names).
+//            tiled copies (box = 128 bytes x 32, 64, 96 or 128 rows, whichever covers the tile's pairs; 128-byte swizzle = the
+//            K-major layout the MMA descriptor names).
 // A pipeline round is two 128-column blocks: the waits and commits of the MMA warps cost about as much as four MMAs each, so
 // they are paid once per eight MMAs.
 // Arithmetic = maple.c:425-458: out = (float)(sum(code*q) - qsum) * qs * s[r]; integer sums are exact.  gate+up scales here;
@@ -41,8 +42,8 @@ extern "C" void k_count_add(long n);
 
 #define UM_TN 128
 #define UM_ASTAGES 2                 /* rounds of two 128-column blocks */
-#define UM_WSTAGES 3
-#define UM_BSTAGES 3                 /* rounds too: 2 x 128 rows x 128 bytes */
+#define UM_WSTAGES 2
+#define UM_BSTAGES 4                 /* rounds too: 2 x 128 rows x 128 bytes */
 #define UM_WBYTES (256 * 128)
 #define UM_BBYTES (2 * UM_TN * 128)
 #define UM_ACOL 256
@@ -68,7 +69,7 @@ __device__ long long g_um_trace[32][8];
 #define TWAIT(id, call) (call)
 #endif
 template <int KB, bool GATEUP>
-__global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap bmap) {
+__global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap4 bmap) {
     extern __shared__ __align__(1024) uint8_t um_smem_raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *wsm = base;                                              // UM_WSTAGES x 32 KB packed weights
@@ -173,9 +174,11 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 for (int kb = 0; kb < KB && live; kb += 2, bcnt++) {
                     const int s = bcnt % UM_BSTAGES;
                     if (!TWAIT(0, mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
-                    mbar_expect_tx(&sh->b_full[s], UM_BBYTES);
-                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES), &bmap, kb * 128, tile.p0, &sh->b_full[s]);
-                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES + UM_TN * 128), &bmap, kb * 128 + 128, tile.p0, &sh->b_full[s]);
+                    // only as many rows as the tile has pairs, in steps of 32 (the MMA reads (cnt + 15) & ~15 <= that many)
+                    const int bi = tile.cnt > 0 ? (tile.cnt - 1) >> 5 : 0;
+                    mbar_expect_tx(&sh->b_full[s], 2 * 128 * 32 * (bi + 1));
+                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES), &bmap.m[bi], kb * 128, tile.p0, &sh->b_full[s]);
+                    tma_load_2d(smem_u32(bsm + s * UM_BBYTES + UM_TN * 128), &bmap.m[bi], kb * 128 + 128, tile.p0, &sh->b_full[s]);
                 }
             }
         }
@@ -385,7 +388,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 }
 
 template <int KB, bool GATEUP>
-static void launch(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) {
+static void launch(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) {
     const size_t smem = (size_t)UM_WSTAGES * UM_WBYTES + UM_BSTAGES * UM_BBYTES + 1024;
     static int sms = 0;
     if (!sms) {
@@ -395,8 +398,8 @@ static void launch(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) {
     expert_umma_kernel<KB, GATEUP><<<sms, 640, smem, st>>>(*a, *bmap);
     k_count_add(1);
 }
-extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) { if (a->max_tiles > 0) launch<16, true>(st, a, bmap); }
-extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap) { if (a->max_tiles > 0) launch<4, false>(st, a, bmap); }
+extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<16, true>(st, a, bmap); }
+extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<4, false>(st, a, bmap); }
 
 // ---- rows of the per-token int8 matrix copied into pair (expert-grouped) order: the B operand the TMA can tile ----
 __global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restrict__ src, const int *__restrict__ rows, int8_t *__restrict__ dst, int np) {

@@ -418,18 +418,26 @@ __global__ void __launch_bounds__(128) group_place_kernel(const unsigned *__rest
     for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = sl[k];
 }
 // Decode batches (up to 256 tokens = 2048 pairs): the whole grouping in one CTA, so that the step costs one launch instead of
-// five.  Thread e owns expert e: it walks the pairs in token order (the table sits in shared memory), which gives the reference's
-// order inside an expert directly; the scan over experts and the per-token sort of the eight pair slots follow in the same CTA.
+// five, and without a serial walk: every pair sets its token's bit in its expert's row of a shared-memory bit table; an expert's
+// count is the population of its row, a pair's place inside its expert the population below its token's bit, which is the
+// reference's order (pairs of an expert in token order).  The scan over experts and the per-token sort of the eight pair slots
+// follow in the same CTA.
 #define GS_MAXTOK 256
+#define GS_WORDS (GS_MAXTOK / 32)
 __global__ void __launch_bounds__(NEXP) group_small_kernel(GroupArgs g) {
-    __shared__ short s_top[GS_MAXTOK * TOPK];
+    __shared__ unsigned s_mask[NEXP][GS_WORDS];
+    __shared__ int s_start[NEXP];
     __shared__ int s_slot[GS_MAXTOK * TOPK];
     __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5, nb = g.nb, np = nb * TOPK;
-    for (int i = e; i < np; i += NEXP) s_top[i] = (short)g.top[i];
+#pragma unroll
+    for (int w = 0; w < GS_WORDS; w++) s_mask[e][w] = 0u;
+    __syncthreads();
+    for (int i = e; i < np; i += NEXP) { const int t = i >> 3; atomicOr(&s_mask[g.top[i]][t >> 5], 1u << (t & 31)); }
     __syncthreads();
     int cnt = 0;
-    for (int i = 0; i < np; i++) cnt += (s_top[i] == e);
+#pragma unroll
+    for (int w = 0; w < GS_WORDS; w++) cnt += __popc(s_mask[e][w]);
     if (g.ecnt) g.ecnt[e] = cnt;
     const int used = cnt > 0, na = (cnt + g.tn_a - 1) / g.tn_a, nb_ = (cnt + g.tn_b - 1) / g.tn_b;
     int c = cnt, u = used, a = na, b = nb_;
@@ -445,16 +453,20 @@ __global__ void __launch_bounds__(NEXP) group_small_kernel(GroupArgs g) {
     for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
     const int start = oc + c - cnt, uidx = ou + u - used, ta0 = oa + a - na, tb0 = ob + b - nb_;
     g.estart[e] = used ? start : -1;
+    s_start[e] = start;
     if (used) {
         g.ue[uidx] = e; g.ustart[uidx] = start;
         for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * g.tn_a, min(g.tn_a, cnt - t * g.tn_a), e}; g.tiles_a[ta0 + t] = m; }
         for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * g.tn_b, min(g.tn_b, cnt - t * g.tn_b), e}; g.tiles_b[tb0 + t] = m; }
-        int r = start;
-        for (int i = 0; i < np; i++) if (s_top[i] == e) {          // pairs in token order
-            g.utok[r] = i >> 3; g.uw[r] = g.topw[i]; if (g.uexp) g.uexp[r] = e; s_slot[i] = r; r++;
-        }
     }
     if (e == NEXP - 1) { const int nu = uidx + used; *g.nu = nu; g.ustart[nu] = start + cnt; *g.ntiles_a = ta0 + na; *g.ntiles_b = tb0 + nb_; }
+    __syncthreads();
+    for (int i = e; i < np; i += NEXP) {                             // every pair finds its place
+        const int x = g.top[i], t = i >> 3, w = t >> 5;
+        int r = s_start[x] + __popc(s_mask[x][w] & ((1u << (t & 31)) - 1u));
+        for (int v = 0; v < w; v++) r += __popc(s_mask[x][v]);
+        g.utok[r] = t; g.uw[r] = g.topw[i]; if (g.uexp) g.uexp[r] = x; s_slot[i] = r;
+    }
     __syncthreads();
     for (int t = e; t < nb; t += NEXP) {                             // tp: the token's eight slots ascending
         int sl[TOPK];
@@ -470,7 +482,7 @@ __global__ void __launch_bounds__(NEXP) group_small_kernel(GroupArgs g) {
 }
 extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
-    if (g->nb <= 128) { group_small_kernel<<<1, NEXP, 0, st>>>(*g); g_launches++; return; }
+    if (g->nb <= GS_MAXTOK) { group_small_kernel<<<1, NEXP, 0, st>>>(*g); g_launches++; return; }
     const int np = g->nb * TOPK;
     cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit rows + the 256 counters behind them
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);

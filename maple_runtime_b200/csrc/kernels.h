@@ -70,9 +70,11 @@ void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 
 /* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */
-/* bmap: tensor map over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down), box 128 x 128 */
-void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
-void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap *bmap);
+/* bmap: tensor maps over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down); m[i] has a box
+ * of 128 bytes x 32 (i + 1) rows, so that a tile of few pairs does not pull the next experts' rows through the memory system */
+typedef struct { TMap m[4]; } TMap4;
+void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
+void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
 
@@ -103,7 +105,6 @@ typedef struct {
     int *total;              /* [1] received pairs */
     MoeTile *tiles_a, *tiles_b; int *ntiles_a, *ntiles_b; int tn_a, tn_b;
 } EpPlanArgs;
-void k_ep_plan(cudaStream_t st, const EpPlanArgs *p);
 typedef struct {
     const int8_t *hq; const float *hqs; const int *hqsum;        /* per token, this rank */
     const int *utok, *uexp, *ustart_of_expert, *dst_base; int np, rank, experts_per_rank;
@@ -124,6 +125,8 @@ typedef struct {
 /* All ranks meet: everything a rank's stream did before is complete and visible before any rank's later work starts.  A wait
  * that lasts longer than timeout_ns stores 41 into *err and returns. */
 void k_ep_exchange(cudaStream_t st, const EpXchArgs *a);
+/* the plan; x != NULL: preceded, in the same kernel, by the rendezvous that exchanges the counts the plan reads */
+void k_ep_plan(cudaStream_t st, const EpPlanArgs *p, const EpXchArgs *x);
 
 void k_synth_experts(cudaStream_t st, uint64_t seed, int L, int e0, int ne, uint8_t *dst);
 

@@ -64,7 +64,7 @@ def check_stages(g, nb, d, exact_fp=True):
             assert rel(got, want) <= TOL, k
 
 
-@pytest.mark.parametrize("nb,stream,norm", [(1, 201, 0), (5, 202, 0), (32, 203, 1), (33, 204, 1), (64, 205, 0), (128, 206, 1)])
+@pytest.mark.parametrize("nb,stream,norm", [(1, 201, 0), (5, 202, 0), (32, 203, 1), (33, 204, 1), (64, 205, 0), (128, 206, 1), (200, 207, 1), (256, 208, 0), (257, 209, 1)])
 def test_layer_all_stages_equal_oracle(nb, stream, norm, layers, oracle, weights):
     """Configs 1 (128-token chunk) and 2 (64 conversations) and the route_small/route_multi boundary."""
     g = layers
