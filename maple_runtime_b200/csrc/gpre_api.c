@@ -38,7 +38,7 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; void *router_t; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
+typedef struct { uint16_t *router, *post_ln; void *router_t, *router_s; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
 
 static struct {
     int ready, maxtok, maxp, mask_words, keep, path, nb_cur, ep_on;
@@ -214,7 +214,7 @@ static int layer_bufs(const char *who, int L) {
     if (L < 0 || L >= GMOE_LAYERS) return fail(who, "layer %d outside 0..%d", L, GMOE_LAYERS - 1);
     LayerDev *l = &S.ly[L];
     if (!l->router) {
-        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->dsp, NEXP * sizeof(void *)) || dmalloc((void **)&l->post_ln, HID * 2) ||
+        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc(&l->router_s, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->dsp, NEXP * sizeof(void *)) || dmalloc((void **)&l->post_ln, HID * 2) ||
             dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs)) || dmalloc((void **)&l->maps, NEXP * sizeof(ExpertMaps)))
             return fail(who, "out of device memory for layer %d", L);
     }
@@ -228,7 +228,7 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     CU("gmoe", cudaMemcpyAsync(l->maps, S.h_maps, NEXP * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     uint16_t ones[HID]; for (int i = 0; i < HID; i++) ones[i] = 0x3F80;
     CU("gmoe", cudaMemcpyAsync(l->router, router, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st));
-    k_router_pack(S.st, l->router, l->router_t);
+    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s);
     CU("gmoe", cudaMemcpyAsync(l->post_ln, post_ln ? post_ln : ones, HID * 2, cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
     for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
@@ -256,7 +256,7 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     if (!r) return fail("gmoe", "out of host memory");
     msynth_router(seed, L, r); msynth_norm(seed, L, nw);
     cudaError_t e1 = cudaMemcpyAsync(l->router, r, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st);
-    k_router_pack(S.st, l->router, l->router_t);
+    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s);
     cudaError_t e2 = cudaMemcpyAsync(l->post_ln, nw, HID * 2, cudaMemcpyHostToDevice, S.st);
     cudaError_t e3 = cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st);
     for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
@@ -359,11 +359,11 @@ static void run_combine(const float *const *dsp, int nb, const float *init, floa
     if (use_umma(nb)) k_combine_wire(S.st, S.wire, S.maxp, dsp, S.uw, S.tp, init, out, nb);
     else k_combine(S.st, S.down, S.uw, S.tp, init, out, nb);
 }
-/* router logits: batches past the decode sizes take the tiled kernel on the re-laid router rows */
+/* router logits: batches past the decode sizes take the tiled kernel, decode batches the one-wait kernel, both on re-laid rows */
 #define ROUTER_TILE_MIN 257
 static void run_router(const LayerDev *l, const float *bias, int nb) {
     if (nb >= ROUTER_TILE_MIN) k_router_logits_tile(S.st, l->router_t, S.hn, S.hT, bias, S.logits, nb, S.err);
-    else k_router_logits(S.st, l->router, S.hn, bias, S.logits, nb);
+    else k_router_logits_small(S.st, l->router_s, S.hn, S.hT, bias, S.logits, nb, S.err);
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {

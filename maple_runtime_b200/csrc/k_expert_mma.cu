@@ -42,8 +42,9 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
     constexpr int TN = NBLK * 8, KB = KCH * 256;            // tokens per tile, bytes of one int8 activation vector
     extern __shared__ __align__(16) uint8_t smem[];          // [KCH][4][TN][4][16]
     const int tile_i = blockIdx.y;
-    if (tile_i >= *a.ntiles) return;
-    const MoeTile tile = a.tiles[tile_i];
+    const int ntiles = *a.ntiles;
+    const MoeTile tile = a.tiles[tile_i < a.max_tiles ? tile_i : 0];      // read beside the count, not after it
+    if (tile_i >= ntiles) return;
     const ExpertPtrs ep = a.tab[tile.ex];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
 
@@ -52,9 +53,10 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
     const uint8_t *wa = (GATEUP ? ep.gc : ep.dc) + (size_t)(r0 + g) * (KB / 4) + t * 16;
     const uint8_t *wb = GATEUP ? ep.uc + (size_t)(r0 + g) * (KB / 4) + t * 16 : wa + 16 * (KB / 4);
     // the weight stream starts before anything else: the first two chunks are on their way while the activations are staged
-    uint4 wq[2][4];
+    constexpr int PF = 2;                                   // chunks in flight (more costs occupancy and loses)
+    uint4 wq[PF][4];
 #pragma unroll
-    for (int p = 0; p < 2; p++) if (p < KCH) {
+    for (int p = 0; p < PF; p++) if (p < KCH) {
         wq[p][0] = ldg_stream(wa + p * 64); wq[p][1] = ldg_stream(wa + 8 * (KB / 4) + p * 64);
         wq[p][2] = ldg_stream(wb + p * 64); wq[p][3] = ldg_stream(wb + 8 * (KB / 4) + p * 64);
     }
@@ -110,10 +112,10 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
 
 #pragma unroll
     for (int c = 0; c < KCH; c++) {
-        const uint4 wa0 = wq[c & 1][0], wa1 = wq[c & 1][1], wb0 = wq[c & 1][2], wb1 = wq[c & 1][3];
-        if (c + 2 < KCH) {   // two chunks in flight while this one is multiplied
-            wq[c & 1][0] = ldg_stream(wa + (c + 2) * 64); wq[c & 1][1] = ldg_stream(wa + 8 * (KB / 4) + (c + 2) * 64);
-            wq[c & 1][2] = ldg_stream(wb + (c + 2) * 64); wq[c & 1][3] = ldg_stream(wb + 8 * (KB / 4) + (c + 2) * 64);
+        const uint4 wa0 = wq[c % PF][0], wa1 = wq[c % PF][1], wb0 = wq[c % PF][2], wb1 = wq[c % PF][3];
+        if (c + PF < KCH) {   // PF chunks in flight while this one is multiplied
+            wq[c % PF][0] = ldg_stream(wa + (c + PF) * 64); wq[c % PF][1] = ldg_stream(wa + 8 * (KB / 4) + (c + PF) * 64);
+            wq[c % PF][2] = ldg_stream(wb + (c + PF) * 64); wq[c % PF][3] = ldg_stream(wb + 8 * (KB / 4) + (c + PF) * 64);
         }
 #pragma unroll
         for (int s = 0; s < 4; s++) {

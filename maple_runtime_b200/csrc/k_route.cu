@@ -1,4 +1,4 @@
-// k_route.cu -- everything of the MoE half that is not a grouped GEMM: RMSNorm + per-token int8, router logits,
+// k_route.cu -- everything of the MoE half that is not a grouped GEMM or the router: RMSNorm + per-token int8,
 // softmax + top-8, grouping of pairs by expert, SiLU-output int8, weighted combine.  sm_100a.
 //
 // Every kernel reproduces the reference's arithmetic operation by operation (order of additions, fused
@@ -85,198 +85,7 @@ extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, 
     norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum); g_launches++;
 }
 
-// ------------------------------------------------------------------------------------------------------------
-// Router logits (maple.c:870-889 job_route_multi, 853-869 job_route_small): logit[b][e] = sum_c W[e][c]*hn[b][c]
-// in the reference's order: lane j of eight accumulates columns j, j+8, ... with one FMA each, and the eight
-// partial sums are added as ((l0+l4)+(l1+l5))+((l2+l6)+(l3+l7)) (hsum, maple.c:117-121).
-// 256 threads = 8 lanes x 32 tile positions; each thread owns a TT x TE register tile for its lane.
-// Shared-memory rows hold 128 columns re-ordered as [lane j][16 steps], lanes 20 floats apart so that the eight
-// lanes of one position read 128 distinct bytes per 16-byte access.
-// ------------------------------------------------------------------------------------------------------------
-#define RT_KC 128
-#define RT_LS 20
-#define RT_ROW (8 * RT_LS + 4)
-template <int TT, int TE, int PT, int PE>
-__global__ void __launch_bounds__(256) router_logits_kernel(const uint16_t *__restrict__ W, const float *__restrict__ hn,
-                                                            const float *__restrict__ bias, float *__restrict__ logits, int nb) {
-    constexpr int BT = TT * PT, BE = TE * PE;
-    static_assert(PT * PE == 32, "32 tile positions");
-    __shared__ __align__(16) float hs[BT * RT_ROW];
-    __shared__ __align__(16) float ws[BE * RT_ROW];
-    const int tid = threadIdx.x, j = tid & 7, pos = tid >> 3, pt = pos % PT, pe = pos / PT;
-    const int b0 = blockIdx.y * BT, e0 = blockIdx.x * BE;
-    float acc[TT][TE];
-#pragma unroll
-    for (int a = 0; a < TT; a++)
-#pragma unroll
-        for (int c = 0; c < TE; c++) acc[a][c] = 0.0f;
-
-    // this thread's share of a 128-column chunk, fetched one chunk ahead of the arithmetic
-    constexpr int NH = (BT * (RT_KC / 4) + 255) / 256, NW = (BE * (RT_KC / 8) + 255) / 256;
-    float4 ph[NH]; uint4 pw[NW];
-    auto fetch = [&](int c0) {
-#pragma unroll
-        for (int k = 0; k < NH; k++) {
-            const int i = tid + 256 * k, r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
-            ph[k] = (i < BT * (RT_KC / 4) && b0 + r < nb) ? *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int k = 0; k < NW; k++) {
-            const int i = tid + 256 * k, r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
-            pw[k] = (i < BE * (RT_KC / 8)) ? *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c) : make_uint4(0, 0, 0, 0);
-        }
-    };
-    fetch(0);
-    for (int c0 = 0; c0 < HID; c0 += RT_KC) {
-        __syncthreads();
-#pragma unroll
-        for (int k = 0; k < NH; k++) {
-            const int i = tid + 256 * k, r = i / (RT_KC / 4), c = (i % (RT_KC / 4)) * 4;
-            if (i < BT * (RT_KC / 4)) {
-                float *d = hs + r * RT_ROW + (c >> 3); const int jj = c & 7;
-                d[(jj + 0) * RT_LS] = ph[k].x; d[(jj + 1) * RT_LS] = ph[k].y; d[(jj + 2) * RT_LS] = ph[k].z; d[(jj + 3) * RT_LS] = ph[k].w;
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < NW; k++) {
-            const int i = tid + 256 * k, r = i / (RT_KC / 8), c = (i % (RT_KC / 8)) * 8;
-            if (i < BE * (RT_KC / 8)) {
-                float *d = ws + r * RT_ROW + (c >> 3); const uint4 v = pw[k];
-                d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
-                d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
-                d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
-                d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
-            }
-        }
-        __syncthreads();
-        if (c0 + RT_KC < HID) fetch(c0 + RT_KC);
-#pragma unroll
-        for (int i4 = 0; i4 < RT_KC / 8 / 4; i4++) {
-            float4 hv[TT], wv[TE];
-#pragma unroll
-            for (int a = 0; a < TT; a++) hv[a] = *reinterpret_cast<const float4 *>(hs + (pt * TT + a) * RT_ROW + j * RT_LS + i4 * 4);
-#pragma unroll
-            for (int c = 0; c < TE; c++) wv[c] = *reinterpret_cast<const float4 *>(ws + (pe * TE + c) * RT_ROW + j * RT_LS + i4 * 4);
-#pragma unroll
-            for (int a = 0; a < TT; a++)
-#pragma unroll
-                for (int c = 0; c < TE; c++) {
-                    acc[a][c] = __fmaf_rn(wv[c].x, hv[a].x, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].y, hv[a].y, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].z, hv[a].z, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].w, hv[a].w, acc[a][c]);
-                }
-        }
-    }
-#pragma unroll
-    for (int a = 0; a < TT; a++)
-#pragma unroll
-        for (int c = 0; c < TE; c++) {
-            float l = acc[a][c];
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 4));   // l_j + l_{j^4}
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 1));   // (l0+l4)+(l1+l5) | (l2+l6)+(l3+l7)
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 2));
-            int b = b0 + pt * TT + a, e = e0 + pe * TE + c;
-            if (j == 0 && b < nb) logits[(size_t)b * NEXP + e] = bias ? __fadd_rn(l, bias[e]) : l;
-        }
-}
-// The prefill variant: a 32-token x 64-expert tile per CTA, each thread an 8 x 8 register tile for its lane j, the four
-// tile positions of a warp arranged 2 x 2 so that every shared-memory row a warp reads feeds two positions (0.5 bytes of
-// shared-memory traffic per FMA, half of what the bandwidth allows at the full FMA rate).  Two CTAs share an SM, one multiplies
-// while the other loads.  Same chain order per (token, expert, lane) as above.
-__global__ void __launch_bounds__(256, 2) router_logits_prefill_kernel(const uint16_t *__restrict__ W, const float *__restrict__ hn,
-                                                                      const float *__restrict__ bias, float *__restrict__ logits, int nb) {
-    constexpr int BT = 32, BE = 64, TT = 8, TE = 8;
-    extern __shared__ __align__(16) float rsm[];
-    float *hs = rsm, *ws = rsm + BT * RT_ROW;
-    const int tid = threadIdx.x, j = tid & 7, pos = tid >> 3, warp = tid >> 5, q = pos & 3;
-    const int tg = (warp & 1) * 2 + (q & 1), eg = (warp >> 1) * 2 + (q >> 1);       // 4 token groups x 8 expert groups; a warp holds 2 x 2 of them
-    const int b0 = blockIdx.y * BT, e0 = blockIdx.x * BE;
-    float acc[TT][TE];
-#pragma unroll
-    for (int a = 0; a < TT; a++)
-#pragma unroll
-        for (int c = 0; c < TE; c++) acc[a][c] = 0.0f;
-    // this thread's share of a chunk: 4 float4 of hidden rows, 2 x 8 bf16 of router rows
-    float4 ph[4]; uint4 pw[4];
-    auto fetch = [&](int c0) {
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int i = tid + 256 * k, r = i >> 5, c = (i & 31) * 4;
-            ph[k] = (b0 + r < nb) ? *reinterpret_cast<const float4 *>(hn + (size_t)(b0 + r) * HID + c0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int i = tid + 256 * k, r = i >> 4, c = (i & 15) * 8;
-            pw[k] = *reinterpret_cast<const uint4 *>(W + (size_t)(e0 + r) * HID + c0 + c);
-        }
-    };
-    auto stash = [&]() {
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int i = tid + 256 * k, r = i >> 5, c = (i & 31) * 4;
-            float *d = hs + r * RT_ROW + (c >> 3); const int jj = c & 7;
-            d[(jj + 0) * RT_LS] = ph[k].x; d[(jj + 1) * RT_LS] = ph[k].y; d[(jj + 2) * RT_LS] = ph[k].z; d[(jj + 3) * RT_LS] = ph[k].w;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int i = tid + 256 * k, r = i >> 4, c = (i & 15) * 8;
-            float *d = ws + r * RT_ROW + (c >> 3); const uint4 v = pw[k];
-            d[0 * RT_LS] = __uint_as_float(v.x << 16); d[1 * RT_LS] = __uint_as_float(v.x & 0xFFFF0000u);
-            d[2 * RT_LS] = __uint_as_float(v.y << 16); d[3 * RT_LS] = __uint_as_float(v.y & 0xFFFF0000u);
-            d[4 * RT_LS] = __uint_as_float(v.z << 16); d[5 * RT_LS] = __uint_as_float(v.z & 0xFFFF0000u);
-            d[6 * RT_LS] = __uint_as_float(v.w << 16); d[7 * RT_LS] = __uint_as_float(v.w & 0xFFFF0000u);
-        }
-    };
-    for (int c0 = 0; c0 < HID; c0 += RT_KC) {
-        fetch(c0);                                   // the co-resident CTA of the SM covers this latency
-        __syncthreads();
-        stash();
-        __syncthreads();
-#pragma unroll
-        for (int i4 = 0; i4 < RT_KC / 8 / 4; i4++) {
-            float4 wv[TE];
-#pragma unroll
-            for (int c = 0; c < TE; c++) wv[c] = *reinterpret_cast<const float4 *>(ws + (eg * TE + c) * RT_ROW + j * RT_LS + i4 * 4);
-#pragma unroll
-            for (int a = 0; a < TT; a++) {
-                const float4 hv = *reinterpret_cast<const float4 *>(hs + (tg * TT + a) * RT_ROW + j * RT_LS + i4 * 4);
-#pragma unroll
-                for (int c = 0; c < TE; c++) {
-                    acc[a][c] = __fmaf_rn(wv[c].x, hv.x, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].y, hv.y, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].z, hv.z, acc[a][c]);
-                    acc[a][c] = __fmaf_rn(wv[c].w, hv.w, acc[a][c]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int a = 0; a < TT; a++)
-#pragma unroll
-        for (int c = 0; c < TE; c++) {
-            float l = acc[a][c];
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 4));
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 1));
-            l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, 2));
-            const int b = b0 + tg * TT + a, e = e0 + eg * TE + c;
-            if (j == 0 && b < nb) logits[(size_t)b * NEXP + e] = bias ? __fadd_rn(l, bias[e]) : l;
-        }
-}
-extern "C" void k_router_logits(cudaStream_t st, const uint16_t *router, const float *hn, const float *bias, float *logits, int nb) {
-    if (nb <= 0) return;
-    if (nb <= 256) {   // few tokens: small tiles so that the grid still covers the SMs
-        dim3 grid(NEXP / 8, (nb + 7) / 8);
-        router_logits_kernel<1, 2, 8, 4><<<grid, 256, 0, st>>>(router, hn, bias, logits, nb);
-    } else {
-        const size_t smem = (size_t)(32 + 64) * RT_ROW * sizeof(float);
-        static bool attr_done = false;
-        if (!attr_done) { cudaFuncSetAttribute(router_logits_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
-        dim3 grid(NEXP / 64, (nb + 31) / 32);
-        router_logits_prefill_kernel<<<grid, 256, smem, st>>>(router, hn, bias, logits, nb);
-    }
-    g_launches++;
-}
+// (Router logits live in k_router_tile.cu.)
 
 // ------------------------------------------------------------------------------------------------------------
 // Softmax + top-8 (maple.c:910-923): one warp per token, lane l holds experts 8l..8l+7.

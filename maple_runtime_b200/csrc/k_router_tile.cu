@@ -194,3 +194,82 @@ extern "C" void k_router_logits_tile(cudaStream_t st, const void *router_t, cons
     }
     k_count_add(2);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode batches (up to 256 tokens).  The arithmetic is a handful of microseconds of dependent multiply-adds (256 per chain), so
+// the kernel is about latency: a CTA owns 8 tokens x 8 experts, fetches all 2048 columns of both in two bulk copies (64 KB of
+// hidden values, 32 KB of bf16 weights, both pre-laid as [column / 32][lane j][4 steps] so that the eight lanes of a position
+// read consecutive 16-byte (8-byte) pieces), waits once, and runs the 64 x 4 steps without another synchronisation.  Two CTAs
+// share an SM, so the 256 CTAs of a 64-token batch are one wave.  256 threads = 8 lanes x 32 positions (8 tokens x 4 expert pairs).
+// ---------------------------------------------------------------------------------------------------------------------
+#define RS_TOK 8
+#define RS_EXP 8
+#define RS_HB (RS_TOK * HID * 4)
+#define RS_WB (RS_EXP * HID * 2)
+// router rows (bf16 [256][2048]) -> [expert][i4 = column / 32][lane j][4 steps]; once per layer
+__global__ void __launch_bounds__(256) router_pack_w_small_kernel(const uint16_t *__restrict__ W, uint2 *__restrict__ WS) {
+    const int o = blockIdx.x * 256 + threadIdx.x, j = o & 7, i4 = (o >> 3) & 63, e = o >> 9;
+    uint16_t v[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) v[k] = W[(size_t)e * HID + (4 * i4 + k) * 8 + j];
+    WS[o] = make_uint2((uint32_t)v[0] | ((uint32_t)v[1] << 16), (uint32_t)v[2] | ((uint32_t)v[3] << 16));
+}
+// hidden rows (fp32 [nb][2048]) -> [token][i4][lane j][4 steps]
+__global__ void __launch_bounds__(256) router_pack_h_small_kernel(const float *__restrict__ hn, float4 *__restrict__ hS, int nb) {
+    const int o = blockIdx.x * 256 + threadIdx.x, j = o & 7, i4 = (o >> 3) & 63, b = o >> 9;
+    if (b >= nb) return;
+    const float *r = hn + (size_t)b * HID + 32 * i4 + j;
+    hS[o] = make_float4(r[0], r[8], r[16], r[24]);
+}
+__global__ void __launch_bounds__(256, 2) router_small_kernel(const uint8_t *__restrict__ WS, const uint8_t *__restrict__ hS, const float *__restrict__ bias,
+                                                             float *__restrict__ logits, int nb, int *err) {
+    extern __shared__ __align__(128) uint8_t rs_sm[];                  // hidden 64 KB, then weights 32 KB
+    __shared__ uint64_t bar; __shared__ int abort_flag;
+    const int tid = threadIdx.x, j = tid & 7, pos = tid >> 3, tok = pos & 7, ep = pos >> 3;
+    const int b0 = blockIdx.y * RS_TOK, e0 = blockIdx.x * RS_EXP, ntok = min(RS_TOK, nb - b0);
+    if (tid == 0) { mbar_init(&bar, 1); abort_flag = 0; mbar_init_fence(); }
+    __syncthreads();
+    if (tid == 0) {
+        mbar_expect_tx(&bar, (uint32_t)(ntok * HID * 4 + RS_WB));
+        bulk_load(smem_u32(rs_sm), hS + (size_t)b0 * HID * 4, (uint32_t)(ntok * HID * 4), &bar);
+        bulk_load(smem_u32(rs_sm + RS_HB), WS + (size_t)e0 * HID * 2, RS_WB, &bar);
+    }
+    const bool ok = mbar_wait(&bar, 0, &abort_flag);
+    float acc0 = 0.0f, acc1 = 0.0f;
+    if (ok && tok < ntok) {
+        const uint8_t *hp = rs_sm + tok * (HID * 4) + j * 16;
+        const uint8_t *w0p = rs_sm + RS_HB + (2 * ep) * (HID * 2) + j * 8, *w1p = w0p + HID * 2;
+#pragma unroll 8
+        for (int i4 = 0; i4 < 64; i4++) {
+            const float4 h = *reinterpret_cast<const float4 *>(hp + i4 * 128);
+            const uint2 a = *reinterpret_cast<const uint2 *>(w0p + i4 * 64), b = *reinterpret_cast<const uint2 *>(w1p + i4 * 64);
+            acc0 = __fmaf_rn(__uint_as_float(a.x << 16), h.x, acc0); acc1 = __fmaf_rn(__uint_as_float(b.x << 16), h.x, acc1);
+            acc0 = __fmaf_rn(__uint_as_float(a.x & 0xFFFF0000u), h.y, acc0); acc1 = __fmaf_rn(__uint_as_float(b.x & 0xFFFF0000u), h.y, acc1);
+            acc0 = __fmaf_rn(__uint_as_float(a.y << 16), h.z, acc0); acc1 = __fmaf_rn(__uint_as_float(b.y << 16), h.z, acc1);
+            acc0 = __fmaf_rn(__uint_as_float(a.y & 0xFFFF0000u), h.w, acc0); acc1 = __fmaf_rn(__uint_as_float(b.y & 0xFFFF0000u), h.w, acc1);
+        }
+    }
+    // the eight lanes of a position sit in one warp: (l0+l4)+(l1+l5) then +(l2+l6)+(l3+l7), the same on every lane
+    float l0 = acc0, l1 = acc1;
+    l0 = __fadd_rn(l0, __shfl_xor_sync(0xffffffffu, l0, 4)); l1 = __fadd_rn(l1, __shfl_xor_sync(0xffffffffu, l1, 4));
+    l0 = __fadd_rn(l0, __shfl_xor_sync(0xffffffffu, l0, 1)); l1 = __fadd_rn(l1, __shfl_xor_sync(0xffffffffu, l1, 1));
+    l0 = __fadd_rn(l0, __shfl_xor_sync(0xffffffffu, l0, 2)); l1 = __fadd_rn(l1, __shfl_xor_sync(0xffffffffu, l1, 2));
+    if (ok && j == 0 && tok < ntok) {
+        const int e = e0 + 2 * ep;
+        float *dst = logits + (size_t)(b0 + tok) * NEXP + e;
+        dst[0] = bias ? __fadd_rn(l0, bias[e]) : l0; dst[1] = bias ? __fadd_rn(l1, bias[e + 1]) : l1;
+    }
+    if (tid == 0 && !ok) atomicExch(err, 31);
+}
+extern "C" void k_router_pack_small(cudaStream_t st, const uint16_t *router, void *router_s) {
+    router_pack_w_small_kernel<<<NEXP * HID / 4 / 256, 256, 0, st>>>(router, (uint2 *)router_s);
+    k_count_add(1);
+}
+extern "C" void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, const float *bias, float *logits, int nb, int *err) {
+    if (nb <= 0) return;
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB); attr_done = true; }
+    router_pack_h_small_kernel<<<nb * 2, 256, 0, st>>>(hn, (float4 *)hS, nb);
+    router_small_kernel<<<dim3(NEXP / RS_EXP, (nb + RS_TOK - 1) / RS_TOK), 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
+    k_count_add(2);
+}
