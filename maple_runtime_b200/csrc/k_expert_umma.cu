@@ -113,22 +113,21 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll
                 for (int rd = 0; rd < 2; rd++, acnt++) {                 // two rounds per weight stage, two 128-column blocks per round
                     const int as = acnt % UM_ASTAGES;
-                    uint32_t r[32];
-                    auto decode = [&](int q) {
+                    uint32_t r[32], r2[32];
+                    auto decode = [&](int q, uint32_t (&o)[32]) {
                         const uint4 v0 = *reinterpret_cast<const uint4 *>(wr + (((2 * q) ^ (R & 7)) << 4));
                         const uint4 v1 = *reinterpret_cast<const uint4 *>(wr + (((2 * q + 1) ^ (R & 7)) << 4));
                         const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
                         for (int sft = 0; sft < 4; sft++)
 #pragma unroll
-                            for (int j = 0; j < 8; j++) r[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
+                            for (int j = 0; j < 8; j++) o[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
                     };
-                    decode(2 * rd);                                      // the first block is ready before the stage is free
+                    decode(2 * rd, r); decode(2 * rd + 1, r2);            // both blocks are ready before the stage is free
                     if (!TWAIT(1, mbar_wait(&sh->a_empty[h][as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp))) { live = false; break; }
                     tc_fence_after();
                     tmem_st32(a_lane + as * 128, r);
-                    decode(2 * rd + 1);
-                    tmem_st32(a_lane + as * 128 + 32, r);
+                    tmem_st32(a_lane + as * 128 + 32, r2);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
