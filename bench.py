@@ -30,6 +30,7 @@ NB, LAYERS, H = 2048, 24, 2048
 EXPERT_BYTES = 798720
 OPS_PER_PAIR = 2 * (2 * 512 * 2048 + 2048 * 512)        # int8 multiply-adds x2 of one (token, expert) pair: 6,291,456
 GU_OPS_PER_PAIR = 2 * 2 * 512 * 2048                     # the gate+up share: 4,194,304
+GU_NCU_TRAFFIC = 169.0e6 + 37.8e6                        # DRAM bytes of one gate+up launch on the 2048-token chunk (ncu, see profiles/)
 METRIC, UNIT = "moe_prefill_tokens_per_s_2048tok_chunk_24_layers", "tokens/s"
 
 
@@ -259,7 +260,9 @@ def main():
     gu_tops = GU_OPS_PER_PAIR * NB * 8 / gu_t / 1e12
     int8_peak = 2.0 * pk["bf16_tflops_sustained"]
     roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary)", "bound": "tensor", "achieved": gu_tops, "peak": int8_peak, "unit": "TOP/s (int8)",
-                "frac": gu_tops / int8_peak, "traffic": None, "launches_timed": int(nlaunch[4]), "avg_launch_us": gu_t * 1e6,
+                "frac": gu_tops / int8_peak, "traffic": GU_NCU_TRAFFIC if args.layers else None, "traffic_unit": "bytes per launch",
+                "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, ncu capture summarised in profiles/prefill_2048tok_2layers_launch_list_and_top_kernels.md (169.0 MB read = weights + int8 rows once, 37.8 MB written)",
+                "launches_timed": int(nlaunch[4]), "avg_launch_us": gu_t * 1e6,
                 "peak_note": f"2 x the {pk['src']} sustained bf16 figure ({pk['bf16_tflops_sustained']} TF/s): no int8 figure is measured on this pool",
                 "weights_gbs": NB and 256 * 2 * 264192 / gu_t / 1e9}
 
@@ -279,7 +282,7 @@ def main():
     if not args.no_decode and rank == 0 and world == 1:
         out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
     if not args.no_cpu and rank == 0:
-        _, _, out["cpu_baseline"] = cpu_reference_arm(8, 1, as_baseline=True)
+        _, _, out["cpu_baseline"] = cpu_reference_arm(400, 1, as_baseline=True, budget_s=12.0)
     if rank == 0:
         print(json.dumps(out))
 
@@ -306,7 +309,8 @@ def decode_leg(g, clib, ml, nl, pk, warm, steps):
     return {"metric": "moe_decode_tokens_per_s_64_conversations", "value": nb * steps / t, "unit": UNIT,
             "ms_per_step": t / steps * 1e3, "used_experts": nu, "bytes_per_layer": layer_bytes,
             "roofline": {"kernel": "gate+up weight stream (register-decode mma.sync)", "bound": "hbm", "achieved": gu_bytes / gu_t / 1e9,
-                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_bytes / gu_t / 1e9 / pk["hbm_gbs"], "traffic": None,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_bytes / gu_t / 1e9 / pk["hbm_gbs"], "traffic": 115.9e6 + 0.3e6, "traffic_unit": "bytes per launch",
+                         "traffic_note": "ncu capture summarised in profiles/decode_64tok_top_kernels.md: every used expert's gate and up bytes once",
                          "avg_launch_us": gu_t * 1e6},
             "layer_hbm_frac": layer_bytes / per_layer / 1e9 / pk["hbm_gbs"],
             "stage_us_per_layer": {name: round(float(s) / (steps * nl) * 1e6, 2) for name, s in zip(g.STAGES, secs)}}
