@@ -67,12 +67,20 @@ int gfull_maxtok(void);
 /* gpu_pre.m:589-594 / maple.c:272: prints the GPU seconds spent in the experts. */
 void gfull_report(void);
 
+/* ---- the attention projections q,k,v,o: the same int8 x ternary product with one matrix and every token in it ----
+ * gpu_pre.m:211-216 / maple.c:264, called at maple.c:1137-1139: adds one matrix (2048 columns, a multiple of 128 rows) to group g
+ * (layer * 2 for q,k,v; layer * 2 + 1 for o); its outputs follow the group's earlier ones.  Copies codes and scales to the card. */
+void gpre_dense_add(int g, const uint8_t *codes, const float *scales, int rows, int cols);
+/* gpu_pre.m:217-233 / maple.c:265, called at maple.c:1141: 0 when every added matrix is on the card, else -1 (the caller then keeps
+ * the projections on the CPU, as the reference does when its buffers do not fit). */
+int gpre_dense_done(int maxtok);
+/* gpu_pre.m:235-256 / maple.c:266: y[nb][rows of the group] = the group's matrices times prep(x[nb][2048]) (tdot_multi of
+ * maple.c:459-470: per-token absmax int8, int32 dot, (float)(tot - qsum) * qs * s[r]).  Returns GPU seconds, -1.0 on error. */
+double gpre_dense(int g, const float *x, int nb, float *y);
+
 /* ---- present so the reference links; not part of the MoE path; each reports "unavailable" ---- */
 int gfull_init(int ctx, int maxtok, int win, const float *norms, const uint16_t *router, const float *cs); /* -1: maple.c:1154-1156 falls back to experts-only */
 double gfull_attn(int L, int glob, float *rl);                                   /* never reached after gfull_init fails; returns 0 */
-void gpre_dense_add(int g, const uint8_t *codes, const float *scales, int rows, int cols);   /* ignored */
-int gpre_dense_done(int maxtok);                                                 /* -1: maple.c:1141 keeps q,k,v,o on the CPU */
-double gpre_dense(int g, const float *x, int nb, float *y);                      /* not reached; returns 0 */
 int gpu_head_init(const uint16_t *w, int rows, int cols);                        /* -1: maple.c:1096 */
 int gpu_head_init_i8(const int8_t *w, const float *scale, int rows, int cols);   /* -1: maple.c:1100 */
 void gpu_head_run(const float *x, float *y);

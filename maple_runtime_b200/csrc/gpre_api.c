@@ -688,9 +688,60 @@ int gfull_init(int ctx, int maxtok, int win, const float *norms, const uint16_t 
     fprintf(stderr, "gfull: attention on the card is not part of this library\n"); return -1;
 }
 double gfull_attn(int L, int glob, float *rl) { (void)L; (void)glob; (void)rl; return 0.0; }
-void gpre_dense_add(int g, const uint8_t *codes, const float *scales, int rows, int cols) { (void)g; (void)codes; (void)scales; (void)rows; (void)cols; }
-int gpre_dense_done(int maxtok) { (void)maxtok; return -1; }
-double gpre_dense(int g, const float *x, int nb, float *y) { (void)g; (void)x; (void)nb; (void)y; return 0.0; }
+/* ---- the attention projections (gpu_pre.m:200-256): every layer's q,k,v (group 2L) and o (group 2L+1) resident on the card.
+ * y[nb][rows of the group] = the group's matrices times prep(x[nb][2048]): the expert product with one matrix and all tokens. */
+#define DGRP 48
+static struct { struct { uint8_t *codes; float *scales; int rows, off; } m[3]; int n, rows; } DG[DGRP];
+static float *DY; static int DY_tok, DY_rows, dense_bad;
+void gpre_dense_add(int g, const uint8_t *codes, const float *scales, int rows, int cols) {
+    if (!S.ready) { fail("gpre", "gpre_dense_add before gpre_init"); dense_bad = 1; return; }
+    if (g < 0 || g >= DGRP || DG[g].n >= 3) { fail("gpre", "gpre_dense_add: group %d", g); dense_bad = 1; return; }
+    if (cols != HID || rows < 128 || (rows % 128)) { fail("gpre", "gpre_dense_add: %d x %d (needs 2048 columns and a multiple of 128 rows)", rows, cols); dense_bad = 1; return; }
+    uint8_t *dc = NULL; float *ds = NULL;
+    if (cudaMalloc((void **)&dc, (size_t)rows * cols / 4) != cudaSuccess || cudaMalloc((void **)&ds, (size_t)rows * 4) != cudaSuccess ||
+        cudaMemcpy(dc, codes, (size_t)rows * cols / 4, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(ds, scales, (size_t)rows * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+        fail("gpre", "gpre_dense_add: no device memory for a %d x %d matrix", rows, cols); dense_bad = 1; return;
+    }
+    const int k = DG[g].n++;
+    DG[g].m[k].codes = dc; DG[g].m[k].scales = ds; DG[g].m[k].rows = rows; DG[g].m[k].off = DG[g].rows; DG[g].rows += rows;
+}
+int gpre_dense_done(int maxtok) {
+    if (!S.ready) return fail("gpre", "gpre_dense_done before gpre_init");
+    if (dense_bad) return -1;                       /* the message of the failed add stands; the caller keeps the projections on the CPU */
+    if (maxtok < 1 || maxtok > S.maxtok) return fail("gpre", "gpre_dense_done: %d tokens, initialised for %d", maxtok, S.maxtok);
+    int ymax = 0; for (int g = 0; g < DGRP; g++) if (DG[g].rows > ymax) ymax = DG[g].rows;
+    if (!ymax) return fail("gpre", "gpre_dense_done: no matrices were added");
+    cudaFree(DY); DY = NULL;
+    if (dmalloc((void **)&DY, (size_t)maxtok * ymax * 4)) return fail("gpre", "no room for the attention projections' results");
+    DY_tok = maxtok; DY_rows = ymax; return 0;
+}
+double gpre_dense(int g, const float *x, int nb, float *y) {
+    if (!S.ready || !DY) { fail("gpre", "gpre_dense before gpre_dense_done"); return -1.0; }
+    if (g < 0 || g >= DGRP || !DG[g].n) { fail("gpre", "gpre_dense: group %d has no matrices", g); return -1.0; }
+    if (nb < 1 || nb > DY_tok) { fail("gpre", "gpre_dense: %d tokens outside 1..%d", nb, DY_tok); return -1.0; }
+    const int ys = DG[g].rows, nt = (nb + 31) / 32;
+    memset(S.h_tab, 0, 3 * sizeof(ExpertPtrs));
+    for (int m = 0; m < DG[g].n; m++) {
+        S.h_tab[m].dc = DG[g].m[m].codes; S.h_tab[m].ds = DG[g].m[m].scales;
+        for (int i = 0; i < nt; i++) { MoeTile t = {m, i * 32, nb - i * 32 < 32 ? nb - i * 32 : 32, m}; S.h_tiles[m * nt + i] = t; }
+    }
+    CUD("gpre", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.tab_call, S.h_tab, 3 * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)DG[g].n * nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.ntiles_a, &nt, 4, cudaMemcpyHostToDevice, S.st));
+    cudaEventRecord(S.e0, S.st);
+    k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);          /* prep of maple.c:184-194 per token */
+    for (int m = 0; m < DG[g].n; m++) {
+        ExpertArgs a; memset(&a, 0, sizeof a);
+        a.tab = S.tab_call; a.tiles = S.tiles_a + (size_t)m * nt; a.ntiles = S.ntiles_a; a.max_tiles = nt; a.err = S.err;
+        a.aq = S.hq; a.aqs = S.hqs; a.aqsum = S.hqsum; a.down = DY + DG[g].m[m].off; a.down_stride = ys;
+        k_dense_mma(S.st, &a, DG[g].m[m].rows);
+    }
+    cudaEventRecord(S.e1, S.st);
+    CUD("gpre", cudaMemcpyAsync(y, DY, (size_t)nb * ys * 4, cudaMemcpyDeviceToHost, S.st));
+    S.nb_cur = nb;
+    return finish("gpre");
+}
 int gpu_head_init(const uint16_t *w, int rows, int cols) { (void)w; (void)rows; (void)cols; return -1; }
 int gpu_head_init_i8(const int8_t *w, const float *scale, int rows, int cols) { (void)w; (void)scale; (void)rows; (void)cols; return -1; }
 void gpu_head_run(const float *x, float *y) { (void)x; (void)y; }

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(128) expert_mma_kernel(ExpertArgs a) {
                 if (a.act_for_down) { const float *s_qs = reinterpret_cast<const float *>(smem + KCH * 4 * TN * 64); qs = s_qs[n]; qsum_p = reinterpret_cast<const int *>(s_qs + TN)[n]; }
                 else { qs = a.aqs[pair]; qsum_p = a.aqsum[pair]; }
                 int da = acc_a[j][k] - qsum_p, db = acc_b[j][k] - qsum_p;
-                float *drow = a.down + (size_t)pair * 2048;
+                float *drow = a.down + (size_t)pair * (a.down_stride ? a.down_stride : 2048);
                 if (a.rx_src) { const int2 sp = a.rx_src[pair]; drow = a.peer_down[sp.x] + (size_t)sp.y * 2048; }   // the row goes to the token's rank
                 drow[rr] = __fmul_rn(__fmul_rn((float)da, qs), sca[k >> 1]);
                 drow[rr + 16] = __fmul_rn(__fmul_rn((float)db, qs), scb[k >> 1]);
@@ -184,4 +184,15 @@ extern "C" void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn) {
 extern "C" void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn) {
     if (a->max_tiles <= 0) return;
     if (tn == 8) launch<2, 1, false>(st, a); else launch<2, 4, false>(st, a);
+}
+
+// The attention projections (gpu_pre.m:200-256 gpre_dense*): the same int8 x 2-bit product with one matrix instead of 256
+// experts and every token in it: K = 2048, two 16-row blocks per warp, 128 rows per CTA, tiles of 32 tokens.
+extern "C" void k_dense_mma(cudaStream_t st, const ExpertArgs *a, int rows) {
+    if (a->max_tiles <= 0 || rows <= 0) return;
+    const size_t smem = (size_t)8 * 4 * 32 * 64 + 32 * 8;
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(expert_mma_kernel<8, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
+    expert_mma_kernel<8, 4, false><<<dim3(rows / 128, a->max_tiles), 128, smem, st>>>(*a);
+    k_count_add(1);
 }

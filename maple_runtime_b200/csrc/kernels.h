@@ -27,7 +27,8 @@ typedef struct {
     float *act;              /* [np][512] */
     /* down inputs */
     const int8_t *aq; const float *aqs; const int *aqsum;          /* per pair */
-    float *down;             /* [np][2048] */
+    float *down;             /* [np][2048], or [np][down_stride] when down_stride != 0 (the dense projections: several matrices side by side) */
+    int down_stride;
     /* decode path: the down kernel quantises the fp32 SiLU outputs itself (no separate pass): act_for_down [np][512] in, and the
      * int8 rows, scales and sums it computed are also stored here for later inspection */
     const float *act_for_down; int8_t *aq_out; float *aqs_out; int *aqsum_out;
@@ -69,6 +70,9 @@ void k_combine(cudaStream_t st, const float *down, const float *uw, const int *t
 
 /* register-decode + mma.sync grouped kernels (any token count; the decode-batch path); tn = 8 or 32 */
 void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
+/* a dense ternary matrix of `rows` rows (a multiple of 128) x 2048 columns as one "expert": tab[tile.ex].dc / .ds = its codes and
+ * row scales; aq/aqs/aqsum = the int8 rows of the tokens (2048 bytes each); results go to down[token * down_stride + row] */
+void k_dense_mma(cudaStream_t st, const ExpertArgs *a, int rows);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 
 /* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */

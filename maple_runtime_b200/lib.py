@@ -132,6 +132,20 @@ class Gpre:
     def set_layer(self, L, router, post_ln, gloc, regs):
         self._chk(self.lib.gmoe_set_layer(L, _p(router), _p(post_ln), _p(gloc), _p(regs)))
 
+    # --- attention projections (gpre_dense_*)
+    def dense_add(self, g, codes, scales, rows, cols):
+        codes = np.ascontiguousarray(codes, np.uint8); scales = np.ascontiguousarray(scales, np.float32)
+        self.lib.gpre_dense_add(g, _p(codes), _p(scales), rows, cols)
+
+    def dense_done(self, maxtok):
+        return self._chk(self.lib.gpre_dense_done(maxtok))
+
+    def dense(self, g, x, rows):
+        nb = x.shape[0]
+        y = np.empty((nb, rows), np.float32)
+        t = self._chk(self.lib.gpre_dense(g, _p(x), nb, _p(y)))
+        return y, t
+
     # --- compute
     def gpre_moe(self, x, nu, loc, regs, ustart, ptok, pw, tp):
         nb = x.shape[0]

@@ -297,3 +297,39 @@ def test_full_chunk_2048_properties(layers, oracle, weights):
     assert np.array_equal(np.sort(tp.ravel()), np.arange(nb * 8))
     sub = x[1000:1010].copy(); g.forward(sub, 0, 1)
     assert same_bits(sub, y[1000:1010])                                  # tokens do not interact
+
+
+def test_dense_projections_equal_reference_statement(layers, clib):
+    """gpre_dense_add / _done / gpre_dense (gpu_pre.m:200-256): q, k, v in one group, o in another; results bit for bit equal to
+    the numpy statement that the CPU suite pins to the reference's tdot.  Ragged token counts, an all-zero token, bad calls."""
+    import dense_ref
+    g = layers
+    rng = np.random.default_rng(23)
+
+    def matrix(rows):
+        codes = rng.choice(np.array([0, 1, 2], np.uint8), size=(rows, 2048), p=[0.3, 0.4, 0.3]).reshape(rows, 16, 4, 32)
+        packed = np.zeros((rows, 16, 32), np.uint8)
+        for k in range(4):
+            packed |= (codes[:, :, k, :] << (2 * k)).astype(np.uint8)
+        return np.ascontiguousarray(packed.reshape(rows, 512)), rng.uniform(0.01, 0.05, rows).astype(np.float32)
+    q, k, v, o = matrix(2048), matrix(512), matrix(512), matrix(2048)
+    for m in (q, k, v):
+        g.dense_add(0, m[0], m[1], m[0].shape[0], 2048)
+    g.dense_add(1, o[0], o[1], 2048, 2048)
+    g.dense_done(2048)
+    for nb in (1, 33, 300):
+        x = rng.standard_normal((nb, 2048)).astype(np.float32) * np.float32(3.0)
+        if nb > 2:
+            x[2] = 0.0
+        y, secs = g.dense(0, x, 3072)
+        want = np.concatenate([dense_ref.dense(m[0], m[1], m[0].shape[0], 2048, x) for m in (q, k, v)], axis=1)
+        assert secs > 0 and same_bits(y, want), f"nb {nb}: rel {rel(y, want):.3e}"
+        y1, _ = g.dense(1, x, 2048)
+        assert same_bits(y1, dense_ref.dense(o[0], o[1], 2048, 2048, x))
+    with pytest.raises(RuntimeError, match="no matrices"):
+        g.dense(5, np.zeros((4, 2048), np.float32), 2048)
+    # the MoE path still works after the projections used its staging buffers
+    xx = np.ascontiguousarray(rng.standard_normal((40, 2048)).astype(np.float32))
+    a = xx.copy(); g.forward(a, 0, 1)
+    b = xx.copy(); g.forward(b, 0, 1)
+    assert same_bits(a, b)

@@ -124,3 +124,29 @@ def test_group_properties(oracle):
     t = tp.reshape(nb, 8)
     assert np.all(np.diff(t, axis=1) > 0) and np.array_equal(np.sort(t.ravel()), np.arange(nb * 8))
     assert all(utok[a] == b for b in range(nb) for a in t[b])
+
+
+def test_dense_projection_statement_equals_reference_tdot(reference):
+    """The numpy statement the GPU dense projections are tested against equals the compiled reference's prep + tdot."""
+    import ctypes as C
+    import dense_ref
+    rng = np.random.default_rng(11)
+    rows, cols, nb = 256, 2048, 5
+    codes = rng.choice(np.array([0, 1, 2], np.uint8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+    packed = np.zeros((rows, cols // 128, 32), np.uint8)
+    g = codes.reshape(rows, cols // 128, 4, 32)
+    for k in range(4):
+        packed |= (g[:, :, k, :] << (2 * k)).astype(np.uint8)
+    packed = np.ascontiguousarray(packed.reshape(rows, cols // 4))
+    scales = rng.uniform(0.01, 0.05, rows).astype(np.float32)
+    x = rng.standard_normal((nb, cols)).astype(np.float32)
+    x[3] = 0.0                                                            # the all-zero vector: qs = 1
+    want = dense_ref.dense(packed, scales, rows, cols, x)
+    lib = reference.lib
+    lib.rh_tdot.restype = C.c_float
+    lib.rh_tdot.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    for b in range(nb):
+        xb = np.ascontiguousarray(x[b])
+        for r in (0, 1, 17, 128, 255):
+            got = np.float32(lib.rh_tdot(packed.ctypes.data, scales.ctypes.data, rows, cols, r, xb.ctypes.data))
+            assert got.tobytes() == want[b, r].tobytes(), (b, r, got, want[b, r])
