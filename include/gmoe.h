@@ -23,6 +23,12 @@ extern "C" {
 /* ---- set-up ------------------------------------------------------------------------------------------------ */
 /* Same as gpre_init(maxtok, 8) (maple.c:1105) plus the routing workspace; maxtok <= GMOE_MAXTOK_LIMIT. */
 int gmoe_init(int maxtok);
+/* A converted checkpoint directory (shard-0000N.bin + layout.bin, maple.c:61-81, layout.py) straight into HBM: layers
+ * file_layer0 .. file_layer0+nl-1 of the directory become layers dst_layer0 .. of this library, through gpre_region and
+ * gmoe_set_layer exactly as maple.c:1106-1131 builds its regions and GLOC; with_dense != 0 also adds every layer's q,k,v (group
+ * 2L) and o (group 2L+1) with gpre_dense_add (call gpre_dense_done afterwards).  0, or -1 with gmoe_load_error(). */
+int gmoe_load_layers(const char *dir, int file_layer0, int nl, int dst_layer0, int with_dense);
+const char *gmoe_load_error(void);
 /* Selects the CUDA device of this process (call before gmoe_init / gpre_init; one process per GPU). */
 int gmoe_set_device(int dev);
 /* Layer L's tables in the reference's own form: router bf16 [256][2048] (Layer.router, maple.c:39), post-attention

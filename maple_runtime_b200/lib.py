@@ -44,7 +44,8 @@ DECLS = {
     "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]),
     "gmoe_ep_unique_id": (i32, [vp]), "gmoe_ep_init": (i32, [i32, i32, vp]), "gmoe_ep_handles": (i32, [vp]), "gmoe_ep_connect": (i32, [vp]),
     "gmoe_ep_forward_dev": (i32, [i32, i32, i32, i32, vp]), "gmoe_ep_forward": (f64, [vp, i32, i32, i32, vp]),
-    "gmoe_ep_allmax": (i32, [vp]), "gmoe_ep_received": (i32, []), "gmoe_ep_timeout_selftest": (i32, [i32]),
+    "gmoe_ep_allmax": (i32, [vp]), "gmoe_load_layers": (i32, [C.c_char_p, i32, i32, i32, i32]), "gmoe_load_error": (C.c_char_p, []),
+    "gmoe_ep_received": (i32, []), "gmoe_ep_timeout_selftest": (i32, [i32]),
     "gmoe_group_noalloc": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
     "gmoe_umma_selftest": (i32, [vp, vp, i32, i32, i32, vp]),
     "gmoe_region_read": (i32, [i32, sz, vp, sz]), "gmoe_region_count": (i32, []),

@@ -87,3 +87,30 @@ def test_host_generator_layout(clib, weights):
     b = ml.synth_zipf_bias(clib, SEED)
     p = np.exp(np.sort(b.astype(np.float64))[::-1]) / 256
     assert abs(p.sum() - 1) < 1e-5 and abs(np.log(p[0] / p[1]) - 1.2 * np.log(2)) < 1e-4
+
+
+def test_loader_rejects_what_it_cannot_read(clib, tmp_path):
+    import ctypes as C
+    clib.gmoe_load_error.restype = C.c_char_p
+    assert clib.gmoe_load_layers(str(tmp_path / "nowhere").encode(), 0, 1, 0, 0) == -1
+    assert b"layout.bin" in clib.gmoe_load_error()
+    (tmp_path / "layout.bin").write_bytes(b"\0" * 100)                      # shorter than one layer's records
+    assert clib.gmoe_load_layers(str(tmp_path).encode(), 0, 1, 0, 0) == -1
+    assert b"no layer 0" in clib.gmoe_load_error()
+    assert clib.gmoe_load_layers(str(tmp_path).encode(), 0, 1, 24, 0) == -1    # layer index outside the library's 24
+
+
+def test_synthetic_directory_has_the_converters_record_order(clib, tmp_path):
+    import struct
+    from maple_runtime_b200 import synth_dir, lib as ml
+    synth_dir.write(str(tmp_path), clib, 7, [3])
+    raw = (tmp_path / "layout.bin").read_bytes()
+    recs = [struct.unpack_from("<BBQQII", raw, 26 * i) for i in range(len(raw) // 26)]
+    assert len(recs) == 3 + 5 + 4 + 3 * 256
+    assert [chr(r[0]) for r in recs[:8]] == list("bbbbbbbb") and all(chr(r[0]) == "t" for r in recs[8:])
+    assert recs[7][4:] == (256, 2048)                                       # the router
+    assert recs[12][4:] == (512, 2048) and recs[14][4:] == (2048, 512)      # expert 0: gate, down
+    k, off = recs[12][1], recs[12][2]
+    shard = (tmp_path / f"shard-{k + 1:05d}.bin").read_bytes()
+    want = np.asarray(ml.synth_experts(clib, 7, 3, 0, 1), np.uint8)
+    assert shard[off:off + 1024] == want[:1024].tobytes() and off % 16 == 0

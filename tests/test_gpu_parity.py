@@ -333,3 +333,26 @@ def test_dense_projections_equal_reference_statement(layers, clib):
     a = xx.copy(); g.forward(a, 0, 1)
     b = xx.copy(); g.forward(b, 0, 1)
     assert same_bits(a, b)
+
+
+def test_loader_reads_a_converted_directory(layers, clib, weights, tmp_path):
+    """gmoe_load_layers walks layout.bin as maple.c:61-81 does and registers per layer and shard one region (maple.c:1106-1131).
+    A directory written in the converter's format from the synthetic generator must behave exactly like the same layer
+    generated on the device; its q,k,v,o matrices arrive as dense groups."""
+    import dense_ref
+    from maple_runtime_b200 import synth_dir
+    g = layers
+    info = synth_dir.write(str(tmp_path), clib, SEED, [1])                  # directory layer 0 = synthetic layer 1 of the fixture
+    assert g.lib.gmoe_load_layers(str(tmp_path).encode(), 0, 1, 7, 1) == 0, g.lib.gmoe_load_error()
+    for nb in (64, 600):
+        x = weights.hidden(320 + nb, nb)
+        a = x.copy(); g.forward(a, 1, 1)
+        b = x.copy(); g.forward(b, 7, 1)
+        assert same_bits(a, b)
+    g.dense_done(2048)
+    x = weights.hidden(333, 40)
+    y, _ = g.dense(14, x, 3072)
+    want = np.concatenate([dense_ref.dense(c, s, c.shape[0], 2048, x) for c, s in info["dense"][0][:3]], axis=1)
+    assert same_bits(y, want)
+    assert g.lib.gmoe_load_layers(str(tmp_path).encode(), 1, 1, 8, 0) == -1 and b"no layer 1" in g.lib.gmoe_load_error()
+    assert g.lib.gmoe_load_layers(str(tmp_path / "nowhere").encode(), 0, 1, 8, 0) == -1
