@@ -176,6 +176,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for small profiling captures (not a bench number)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--zipf", action="store_true", help="skewed routing: a per-expert logit bias from a Zipf(s=1.2) ranking (BASELINE config 4); not the headline line")
     args = ap.parse_args()
     rank, local, world = dist_env()
     if args.impl == "reference":
@@ -194,14 +195,17 @@ def main():
         from maple_runtime_b200 import ep
         ep.setup(g, rank, world, gather_obj(dist))
 
+    bias = ml.synth_zipf_bias(clib, SEED) if args.zipf else None
+    bptr = bias.ctypes.data if bias is not None else None
+
     def forward_chunk(c):
         if world > 1:
-            g._chk(clib.gmoe_ep_forward_dev(c, NB, 0, nl, None))
+            g._chk(clib.gmoe_ep_forward_dev(c, NB, 0, nl, bptr))
         else:
-            g._chk(clib.gmoe_forward_chunk(c, NB, 0, nl, None))
+            g._chk(clib.gmoe_forward_chunk(c, NB, 0, nl, bptr))
 
     def forward_host(ptr):
-        return g._chk(clib.gmoe_ep_forward(ptr, NB, 0, nl, None) if world > 1 else clib.gmoe_forward(ptr, NB, 0, nl, None))
+        return g._chk(clib.gmoe_ep_forward(ptr, NB, 0, nl, bptr) if world > 1 else clib.gmoe_forward(ptr, NB, 0, nl, bptr))
     nring = 4
     ring = np.concatenate([ml.synth_hidden(clib, SEED, 2000 + rank * 16 + c, NB) for c in range(nring)])
     g._chk(clib.gmoe_chunks_upload(ring.ctypes.data, NB, nring))
@@ -272,6 +276,8 @@ def main():
            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": NB * H * 4, "d2h_bytes_per_step": NB * H * 4},
            "roofline": roofline, "stage_us_per_layer": breakdown, "wall_s_timed_region": wall,
            "whole_path_int8_tops": OPS_PER_PAIR * NB * 8 * nl * args.steps / t_dev / 1e12}
+    if args.zipf:
+        out["config"]["routing"] = "router logits + per-expert bias ln(256 p_e), p_e ~ rank^-1.2 over a seeded permutation (skewed load); not the headline configuration"
     if nl != LAYERS:
         out["config"]["layers"] = nl
         out["note"] = "reduced layer count: a profiling run, not a benchmark number"
