@@ -689,54 +689,78 @@ int gfull_init(int ctx, int maxtok, int win, const float *norms, const uint16_t 
 }
 double gfull_attn(int L, int glob, float *rl) { (void)L; (void)glob; (void)rl; return 0.0; }
 /* ---- the attention projections (gpu_pre.m:200-256): every layer's q,k,v (group 2L) and o (group 2L+1) resident on the card.
- * y[nb][rows of the group] = the group's matrices times prep(x[nb][2048]): the expert product with one matrix and all tokens. */
+ * y[nb][rows of the group] = the group's matrices times prep(x[nb][2048]): the expert product with one matrix and all tokens.
+ * gpre_dense_add copies into a host staging area (the caller's memory need not outlive the call, as with the reference);
+ * gpre_dense_done puts every group's matrices side by side on the card, so that a group is one matrix of all its rows. */
 #define DGRP 48
-static struct { struct { uint8_t *codes; float *scales; int rows, off; } m[3]; int n, rows; } DG[DGRP];
+static struct {
+    uint8_t *hcodes; float *hscales;            /* staged on the host until gpre_dense_done */
+    uint8_t *codes; float *scales;              /* on the card: [rows][512] codes, [rows] scales */
+    int rows, staged; ExpertMaps maps;          /* maps.down: the 3-D map of the tcgen05 kernel (rows a multiple of 256) */
+} DG[DGRP];
 static float *DY; static int DY_tok, DY_rows, dense_bad;
+static TMap4 bmap_tok;                          /* the tokens' int8 rows [maxtok][2048] as the B operand */
 void gpre_dense_add(int g, const uint8_t *codes, const float *scales, int rows, int cols) {
     if (!S.ready) { fail("gpre", "gpre_dense_add before gpre_init"); dense_bad = 1; return; }
-    if (g < 0 || g >= DGRP || DG[g].n >= 3) { fail("gpre", "gpre_dense_add: group %d", g); dense_bad = 1; return; }
+    if (g < 0 || g >= DGRP || DG[g].codes) { fail("gpre", "gpre_dense_add: group %d (outside 0..%d or already on the card)", g, DGRP - 1); dense_bad = 1; return; }
     if (cols != HID || rows < 128 || (rows % 128)) { fail("gpre", "gpre_dense_add: %d x %d (needs 2048 columns and a multiple of 128 rows)", rows, cols); dense_bad = 1; return; }
-    uint8_t *dc = NULL; float *ds = NULL;
-    if (cudaMalloc((void **)&dc, (size_t)rows * cols / 4) != cudaSuccess || cudaMalloc((void **)&ds, (size_t)rows * 4) != cudaSuccess ||
-        cudaMemcpy(dc, codes, (size_t)rows * cols / 4, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(ds, scales, (size_t)rows * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
-        fail("gpre", "gpre_dense_add: no device memory for a %d x %d matrix", rows, cols); dense_bad = 1; return;
-    }
-    const int k = DG[g].n++;
-    DG[g].m[k].codes = dc; DG[g].m[k].scales = ds; DG[g].m[k].rows = rows; DG[g].m[k].off = DG[g].rows; DG[g].rows += rows;
+    const size_t old = (size_t)DG[g].rows, add = (size_t)rows;
+    uint8_t *hc = realloc(DG[g].hcodes, (old + add) * (HID / 4)); float *hs = realloc(DG[g].hscales, (old + add) * 4);
+    if (hc) DG[g].hcodes = hc;
+    if (hs) DG[g].hscales = hs;
+    if (!hc || !hs) { fail("gpre", "gpre_dense_add: out of host memory"); dense_bad = 1; return; }
+    memcpy(hc + old * (HID / 4), codes, add * (HID / 4)); memcpy(hs + old, scales, add * 4);
+    DG[g].rows += rows; DG[g].staged = 1;
 }
 int gpre_dense_done(int maxtok) {
     if (!S.ready) return fail("gpre", "gpre_dense_done before gpre_init");
     if (dense_bad) return -1;                       /* the message of the failed add stands; the caller keeps the projections on the CPU */
     if (maxtok < 1 || maxtok > S.maxtok) return fail("gpre", "gpre_dense_done: %d tokens, initialised for %d", maxtok, S.maxtok);
-    int ymax = 0; for (int g = 0; g < DGRP; g++) if (DG[g].rows > ymax) ymax = DG[g].rows;
+    int ymax = 0;
+    for (int g = 0; g < DGRP; g++) {
+        if (DG[g].rows > ymax) ymax = DG[g].rows;
+        if (!DG[g].staged) continue;
+        const size_t cb = (size_t)DG[g].rows * (HID / 4), sb = (size_t)DG[g].rows * 4;
+        if (dmalloc((void **)&DG[g].codes, cb) || dmalloc((void **)&DG[g].scales, sb)) return fail("gpre", "no room for the attention projections of group %d", g);
+        CU("gpre", cudaMemcpy(DG[g].codes, DG[g].hcodes, cb, cudaMemcpyHostToDevice));
+        CU("gpre", cudaMemcpy(DG[g].scales, DG[g].hscales, sb, cudaMemcpyHostToDevice));
+        free(DG[g].hcodes); free(DG[g].hscales); DG[g].hcodes = NULL; DG[g].hscales = NULL; DG[g].staged = 0;
+        if (DG[g].rows % 256 == 0) {   /* [rows/2 row pairs][2 parities][512 bytes], box = 128 row pairs x 1 parity x 128 bytes */
+            cuuint64_t gdim[3] = {HID / 4, 2, (cuuint64_t)DG[g].rows / 2}, gstride[2] = {HID / 4, HID / 2};
+            cuuint32_t box[3] = {128, 1, 128}, estr[3] = {1, 1, 1};
+            CUresult r = g_encode((CUtensorMap *)&DG[g].maps.down, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, DG[g].codes, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail("gpre", "cuTensorMapEncodeTiled failed (%d) for the projections of group %d", (int)r, g);
+        }
+    }
     if (!ymax) return fail("gpre", "gpre_dense_done: no matrices were added");
-    cudaFree(DY); DY = NULL;
-    if (dmalloc((void **)&DY, (size_t)maxtok * ymax * 4)) return fail("gpre", "no room for the attention projections' results");
-    DY_tok = maxtok; DY_rows = ymax; return 0;
+    if (!DY || maxtok > DY_tok || ymax > DY_rows) {
+        cudaFree(DY); DY = NULL;
+        if (dmalloc((void **)&DY, (size_t)maxtok * ymax * 4)) return fail("gpre", "no room for the attention projections' results");
+        DY_tok = maxtok; DY_rows = ymax;
+    }
+    for (int i = 0; i < 4; i++) if (tmap_bytes_2d("gpre", &bmap_tok.m[i], S.hq, HID, (uint64_t)S.maxtok, HID, 128, 32 * (i + 1))) return -1;
+    return 0;
 }
 double gpre_dense(int g, const float *x, int nb, float *y) {
     if (!S.ready || !DY) { fail("gpre", "gpre_dense before gpre_dense_done"); return -1.0; }
-    if (g < 0 || g >= DGRP || !DG[g].n) { fail("gpre", "gpre_dense: group %d has no matrices", g); return -1.0; }
+    if (g < 0 || g >= DGRP || !DG[g].codes) { fail("gpre", "gpre_dense: group %d has no matrices on the card", g); return -1.0; }
     if (nb < 1 || nb > DY_tok) { fail("gpre", "gpre_dense: %d tokens outside 1..%d", nb, DY_tok); return -1.0; }
-    const int ys = DG[g].rows, nt = (nb + 31) / 32;
-    memset(S.h_tab, 0, 3 * sizeof(ExpertPtrs));
-    for (int m = 0; m < DG[g].n; m++) {
-        S.h_tab[m].dc = DG[g].m[m].codes; S.h_tab[m].ds = DG[g].m[m].scales;
-        for (int i = 0; i < nt; i++) { MoeTile t = {m, i * 32, nb - i * 32 < 32 ? nb - i * 32 : 32, m}; S.h_tiles[m * nt + i] = t; }
-    }
+    const int ys = DG[g].rows, um = nb >= 512 && ys % 256 == 0, tn = um ? UMMA_TN : 32, nt = (nb + tn - 1) / tn;
+    memset(S.h_tab, 0, sizeof(ExpertPtrs));
+    S.h_tab[0].dc = DG[g].codes; S.h_tab[0].ds = DG[g].scales;
+    for (int i = 0; i < nt; i++) { MoeTile t = {0, i * tn, nb - i * tn < tn ? nb - i * tn : tn, 0}; S.h_tiles[i] = t; }
     CUD("gpre", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
-    CUD("gpre", cudaMemcpyAsync(S.tab_call, S.h_tab, 3 * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
-    CUD("gpre", cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)DG[g].n * nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.tab_call, S.h_tab, sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.maps_call, &DG[g].maps, sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
+    CUD("gpre", cudaMemcpyAsync(S.tiles_a, S.h_tiles, (size_t)nt * sizeof(MoeTile), cudaMemcpyHostToDevice, S.st));
     CUD("gpre", cudaMemcpyAsync(S.ntiles_a, &nt, 4, cudaMemcpyHostToDevice, S.st));
     cudaEventRecord(S.e0, S.st);
     k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);          /* prep of maple.c:184-194 per token */
-    for (int m = 0; m < DG[g].n; m++) {
-        ExpertArgs a; memset(&a, 0, sizeof a);
-        a.tab = S.tab_call; a.tiles = S.tiles_a + (size_t)m * nt; a.ntiles = S.ntiles_a; a.max_tiles = nt; a.err = S.err;
-        a.aq = S.hq; a.aqs = S.hqs; a.aqsum = S.hqsum; a.down = DY + DG[g].m[m].off; a.down_stride = ys;
-        k_dense_mma(S.st, &a, DG[g].m[m].rows);
-    }
+    ExpertArgs a; memset(&a, 0, sizeof a);
+    a.tab = S.tab_call; a.maps = S.maps_call; a.tiles = S.tiles_a; a.ntiles = S.ntiles_a; a.max_tiles = nt; a.err = S.err;
+    a.aq = S.hq; a.aqs = S.hqs; a.aqsum = S.hqsum; a.down = DY; a.down_stride = ys; a.dense_mblocks = ys / 256;
+    if (um) k_dense_umma(S.st, &a, &bmap_tok); else k_dense_mma(S.st, &a, ys);
     cudaEventRecord(S.e1, S.st);
     CUD("gpre", cudaMemcpyAsync(y, DY, (size_t)nb * ys * 4, cudaMemcpyDeviceToHost, S.st));
     S.nb_cur = nb;

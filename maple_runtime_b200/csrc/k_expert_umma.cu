@@ -68,7 +68,7 @@ __device__ long long g_um_trace[32][8];
 #else
 #define TWAIT(id, call) (call)
 #endif
-template <int KB, bool GATEUP>
+template <int KB, int MODE>
 __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap4 bmap) {
     extern __shared__ __align__(1024) uint8_t um_smem_raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)um_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -77,7 +77,9 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     __shared__ UmShared sh_static;                                    // static, so that the compiler knows these accesses are shared-memory ones
     UmShared *sh = &sh_static;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int MB = GATEUP ? 4 : 8, NSB = KB / 4;
+    constexpr bool GATEUP = MODE == 0, DENSE = MODE == 2;
+    const int MB = GATEUP ? 4 : (DENSE ? a.dense_mblocks : 8);      // 256-row blocks of the matrix (gate+up: 128 + 128)
+    constexpr int NSB = KB / 4;
     const int nitems = *a.ntiles * MB;
     volatile int *abortp = &sh->abort_flag;
 
@@ -156,8 +158,8 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                         tma_load_2d(dst, &em->gate, sb * 128, mb * 128, &sh->w_full[ws]);
                         tma_load_2d(dst + 128 * 128, &em->up, sb * 128, mb * 128, &sh->w_full[ws]);
                     } else {
-                        tma_load_3d(dst, &em->down, 0, 0, mb * 128, &sh->w_full[ws]);             // the even rows of the 256-row block
-                        tma_load_3d(dst + 128 * 128, &em->down, 0, 1, mb * 128, &sh->w_full[ws]);   // the odd rows
+                        tma_load_3d(dst, &em->down, sb * 128, 0, mb * 128, &sh->w_full[ws]);             // the even rows of the 256-row block
+                        tma_load_3d(dst + 128 * 128, &em->down, sb * 128, 1, mb * 128, &sh->w_full[ws]);   // the odd rows
                     }
                 }
             }
@@ -240,12 +242,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             long long tq0 = clock64();
 #endif
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + 2 * row;      // down: accumulator 0 holds row r0, accumulator 1 row r0 + 1
-            const float s0 = GATEUP ? ep.gs[r0] : 0.0f, s1 = GATEUP ? ep.us[r0] : 0.0f;
+            const float s0 = GATEUP ? ep.gs[r0] : (DENSE ? ep.ds[r0] : 0.0f), s1 = GATEUP ? ep.us[r0] : (DENSE ? ep.ds[r0 + 1] : 0.0f);
             __syncwarp();
             for (int n = lane; n < N; n += 32) {
                 const int pair = tile.p0 + (n < cnt ? n : 0), t = (GATEUP && a.ptok) ? a.ptok[pair] : pair;
-                sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : 32768 - a.aqsum[t];
-                if (!GATEUP && a.rx_src) { const int2 sp = a.rx_src[pair]; sh->m_dst[ew][n] = (unsigned long long)(uintptr_t)(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH); }
+                sh->m_qs[ew][n] = GATEUP ? a.hqs[t] : a.aqs[t]; sh->m_qsum[ew][n] = GATEUP ? a.hqsum[t] : (DENSE ? a.aqsum[t] : 32768 - a.aqsum[t]);
+                if (MODE == 1 && a.rx_src) { const int2 sp = a.rx_src[pair]; sh->m_dst[ew][n] = (unsigned long long)(uintptr_t)(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH); }
             }
             __syncwarp();
 #ifdef UMMA_TRACE
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                     if (lane == 0) mbar_arrive(&sh->acc_empty);
                 }
                 const int lim = cnt - c0;                                 // tokens of this piece that exist
-                if (GATEUP) {
+                if (GATEUP || DENSE) {
                     float o0[16], o1[16];
                     {   // scale and code-sum correction of the piece's 16 tokens: eight 128-bit shared-memory reads
                         const int4 *qsv = reinterpret_cast<const int4 *>(&sh->m_qsum[ew][c0]);
@@ -288,6 +290,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                                 v0[j] = (uint32_t)d0; v1[j] = (uint32_t)d1;
                             }
                         }
+                    }
+                    if (DENSE) {      // fp32 rows of the projection: this thread's two neighbouring rows of every token of the piece
+                        float *dp = a.down + (size_t)(tile.p0 + c0) * a.down_stride + r0;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) if (j < lim) *reinterpret_cast<float2 *>(dp + (size_t)j * a.down_stride) = make_float2(o0[j], o1[j]);
+                        continue;
                     }
                     // one base pointer per thread; the token index only adds a constant, so a store is one instruction
                     float *gp = a.gate + (size_t)(tile.p0 + c0) * 512 + r0, *up_ = a.up + (size_t)(tile.p0 + c0) * 512 + r0;
@@ -386,19 +394,21 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     }
 }
 
-template <int KB, bool GATEUP>
+template <int KB, int MODE>
 static void launch(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) {
     const size_t smem = (size_t)UM_WSTAGES * UM_WBYTES + UM_BSTAGES * UM_BBYTES + 1024;
     static int sms = 0;
     if (!sms) {
         int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaFuncSetAttribute(expert_umma_kernel<KB, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(expert_umma_kernel<KB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    expert_umma_kernel<KB, GATEUP><<<sms, 640, smem, st>>>(*a, *bmap);
+    expert_umma_kernel<KB, MODE><<<sms, 640, smem, st>>>(*a, *bmap);
     k_count_add(1);
 }
-extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<16, true>(st, a, bmap); }
-extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<4, false>(st, a, bmap); }
+extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<16, 0>(st, a, bmap); }
+extern "C" void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<4, 1>(st, a, bmap); }
+/* dense projections: tab[ex].ds / maps[ex].down of a matrix of 256 * a->dense_mblocks rows x 2048 columns, B rows = the tokens' int8 rows */
+extern "C" void k_dense_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<16, 2>(st, a, bmap); }
 
 // ---- rows of the per-token int8 matrix copied into pair (expert-grouped) order: the B operand the TMA can tile ----
 __global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restrict__ src, const int *__restrict__ rows, int8_t *__restrict__ dst, int np) {

@@ -29,6 +29,7 @@ typedef struct {
     const int8_t *aq; const float *aqs; const int *aqsum;          /* per pair */
     float *down;             /* [np][2048], or [np][down_stride] when down_stride != 0 (the dense projections: several matrices side by side) */
     int down_stride;
+    int dense_mblocks;       /* k_dense_umma: 256-row blocks of the matrix */
     /* decode path: the down kernel quantises the fp32 SiLU outputs itself (no separate pass): act_for_down [np][512] in, and the
      * int8 rows, scales and sums it computed are also stored here for later inspection */
     const float *act_for_down; int8_t *aq_out; float *aqs_out; int *aqsum_out;
@@ -81,6 +82,9 @@ void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 typedef struct { TMap m[4]; } TMap4;
 void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
+/* a dense matrix (rows a multiple of 256, 2048 columns) on the same kernel: maps[ex].down = its 3-D map (even / odd rows), tab[ex].ds = row
+ * scales, bmap over the tokens' int8 rows, tiles of up to 128 tokens; fp32 results to down[token * down_stride + row] */
+void k_dense_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
 

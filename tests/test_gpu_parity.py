@@ -317,7 +317,7 @@ def test_dense_projections_equal_reference_statement(layers, clib):
         g.dense_add(0, m[0], m[1], m[0].shape[0], 2048)
     g.dense_add(1, o[0], o[1], 2048, 2048)
     g.dense_done(2048)
-    for nb in (1, 33, 300):
+    for nb in (1, 33, 300, 512, 700):                                     # from 512 tokens on the tcgen05 kernel takes the group
         x = rng.standard_normal((nb, 2048)).astype(np.float32) * np.float32(3.0)
         if nb > 2:
             x[2] = 0.0
