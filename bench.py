@@ -287,10 +287,33 @@ def main():
         out["ep_received_pairs_last_layer"] = [int(v) for v in gather_obj(dist)(clib.gmoe_ep_received())]
     if not args.no_decode and rank == 0 and world == 1:
         out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
+        out["dense_projections"] = dense_leg(g, ml, pk, warm, args.steps)
     if not args.no_cpu and rank == 0:
         _, _, out["cpu_baseline"] = cpu_reference_arm(400, 1, as_baseline=True, budget_s=12.0)
     if rank == 0:
         print(json.dumps(out))
+
+
+def dense_leg(g, ml, pk, warm, steps):
+    """The attention projections of one layer on the 2048-token chunk (gpre_dense, gpu_pre.m:235-256): q,k,v as one group of 3072
+    rows and o (2048 rows), synthetic ternary matrices; GPU seconds of the call (per-token int8 + the grouped kernel), host copies
+    outside.  Reported beside the headline, not part of it."""
+    rng = np.random.default_rng(SEED & 0xFFFFFFFF)
+
+    def matrix(rows):   # codes 0..2 in every 2-bit field (never 3), scales as for the experts
+        c = rng.integers(0, 3, size=(rows, 512, 4), dtype=np.uint8)
+        return (c[:, :, 0] | (c[:, :, 1] << 2) | (c[:, :, 2] << 4) | (c[:, :, 3] << 6)).astype(np.uint8), rng.uniform(0.01, 0.05, rows).astype(np.float32)
+    for rows in (2048, 512, 512):
+        g.dense_add(0, *matrix(rows), rows, 2048)
+    g.dense_add(1, *matrix(2048), 2048, 2048)
+    g.dense_done(NB)
+    x = ml.synth_hidden(g.lib, SEED, 4000, NB)
+    out = {}
+    for name, grp, rows in (("qkv", 0, 3072), ("o", 1, 2048)):
+        ts = [g.dense(grp, x, rows)[1] for _ in range(warm + steps)][warm:]
+        t = sum(ts) / len(ts)
+        out[name] = {"rows": rows, "us": t * 1e6, "int8_tops": 2.0 * rows * 2048 * NB / t / 1e12, "frac_of_2x_bf16_sustained": 2.0 * rows * 2048 * NB / t / 1e12 / (2.0 * pk["bf16_tflops_sustained"])}
+    return out
 
 
 def decode_leg(g, clib, ml, nl, pk, warm, steps):
