@@ -93,6 +93,9 @@ extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, 
 // of "first strict maximum" (lowest index wins a tie); weights divided by (their sum in selection order + 1e-20f).
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ logits, int *__restrict__ top, float *__restrict__ topw, int nb) {
+    __shared__ unsigned long long tab[32];                  // the expf table beside the arithmetic (lane-varying index)
+    if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
+    __syncthreads();
     const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (b >= nb) return;
     const float4 *lr = reinterpret_cast<const float4 *>(logits + (size_t)b * NEXP + lane * 8);
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ log
 #pragma unroll
     for (int o = 16; o; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, mx, o); mx = t > mx ? t : mx; }
 #pragma unroll
-    for (int i = 0; i < 8; i++) p[i] = dev_expf(__fsub_rn(p[i], mx));
+    for (int i = 0; i < 8; i++) p[i] = dev_expf_tab(__fsub_rn(p[i], mx), tab);
     float run = 0.0f;
     for (int l = 0; l < 32; l++) {
         if (lane == l) {
@@ -115,21 +118,26 @@ __global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ log
     }
 #pragma unroll
     for (int i = 0; i < 8; i++) p[i] = __fdiv_rn(p[i], run);
+    // Eight rounds of "first strict maximum" (maple.c:917-921).  Probabilities are >= +0, so their bit patterns order like the
+    // values: key = bits + 1, a taken entry becomes 0.  One redux.sync gives the warp's maximum, the lowest lane holding it (and
+    // the lowest of its eight entries) is the first maximum in expert order.
+    unsigned key[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) key[i] = __float_as_uint(p[i]) + 1u;
     float tsum = 0.0f, wsel = 0.0f; int isel = 0;
     for (int k = 0; k < TOPK; k++) {
-        float bv = p[0]; int bi = 0;
+        unsigned lk = key[0];
 #pragma unroll
-        for (int i = 1; i < 8; i++) if (p[i] > bv) { bv = p[i]; bi = i; }
-        int be = lane * 8 + bi;
+        for (int i = 1; i < 8; i++) lk = max(lk, key[i]);
+        const unsigned m = __reduce_max_sync(0xffffffffu, lk);
+        const int src = __ffs(__ballot_sync(0xffffffffu, lk == m)) - 1;
+        int bi = 7;
 #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-        }
-        if ((be >> 3) == lane) {
+        for (int i = 6; i >= 0; i--) if (key[i] == m) bi = i;
+        const int be = __shfl_sync(0xffffffffu, lane * 8 + bi, src);
+        const float bv = __uint_as_float(m - 1u);
 #pragma unroll
-            for (int i = 0; i < 8; i++) if (i == (be & 7)) p[i] = -1.0f;
-        }
+        for (int i = 0; i < 8; i++) if (lane == src && i == bi) key[i] = 0u;
         tsum = __fadd_rn(tsum, bv);
         if (lane == k) { wsel = bv; isel = be; }
     }
