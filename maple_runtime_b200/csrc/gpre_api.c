@@ -361,15 +361,21 @@ static void run_combine(const float *const *dsp, int nb, const float *init, floa
 }
 /* router logits: batches past the decode sizes take the tiled kernel, decode batches the one-wait kernel, both on re-laid rows */
 #define ROUTER_TILE_MIN 257
-static void run_router(const LayerDev *l, const float *bias, int nb) {
+static void run_router_relaid(const LayerDev *l, const float *bias, int nb, int relaid) {   /* relaid: the norm kernel already wrote S.hT */
     if (nb >= ROUTER_TILE_MIN) k_router_logits_tile(S.st, l->router_t, S.hn, S.hT, bias, S.logits, nb, S.err);
-    else k_router_logits_small(S.st, l->router_s, S.hn, S.hT, bias, S.logits, nb, S.err);
+    else k_router_logits_small(S.st, l->router_s, S.hn, S.hT, relaid, bias, S.logits, nb, S.err);
+}
+static void run_router(const LayerDev *l, const float *bias, int nb) { run_router_relaid(l, bias, nb, 0); }
+/* norm + int8 of the layer's input; decode batches also get the router's layout in the same pass */
+static int run_norm(const float *x, const uint16_t *w, int nb) {
+    if (nb < ROUTER_TILE_MIN) { k_norm_prep_relaid(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, (float *)S.hT, nb); return 1; }
+    k_norm_prep(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, nb); return 0;
 }
 /* the MoE half of layer L on the device buffers: norm != 0: x -> hn -> ... -> x += ; else hn -> ... -> y */
 static void run_layer(int L, int nb, int norm, const float *bias) {
     LayerDev *l = &S.ly[L];
-    prof_begin(0); k_norm_prep(S.st, norm ? S.x : S.hn, norm ? l->post_ln : NULL, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
-    prof_begin(1); run_router(l, bias, nb); prof_end(1);
+    prof_begin(0); const int relaid = run_norm(norm ? S.x : S.hn, norm ? l->post_ln : NULL, nb); prof_end(0);
+    prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3); run_group(nb); prof_end(3);
     run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 7);
@@ -901,8 +907,8 @@ static int ep_layer_scales(int L) {
 static int run_layer_ep(int L, int nb, const float *bias) {
     LayerDev *l = &S.ly[L];
     const int tn = tile_tn(nb), um = use_umma(nb);
-    prof_begin(0); k_norm_prep(S.st, S.x, l->post_ln, S.hn, S.hq, S.hqs, S.hqsum, nb); prof_end(0);
-    prof_begin(1); run_router(l, bias, nb); prof_end(1);
+    prof_begin(0); const int relaid = run_norm(S.x, l->post_ln, nb); prof_end(0);
+    prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
     prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     prof_begin(3);
     run_group(nb);

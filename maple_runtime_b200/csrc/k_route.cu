@@ -25,9 +25,10 @@ extern "C" void k_count_add(long n) { g_launches += n; }
 // The sum of squares is accumulated in double like the reference; the tree order differs from its left-to-right
 // order only below double precision, which the conversion to float absorbs.
 // ------------------------------------------------------------------------------------------------------------
+// hS != NULL: the normalised row is also stored as the decode router wants it, [column / 32][lane j][4 steps] (k_router_tile.cu).
 __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w,
                                                         float *__restrict__ hn, int8_t *__restrict__ q,
-                                                        float *__restrict__ qs, int *__restrict__ qsum) {
+                                                        float *__restrict__ qs, int *__restrict__ qsum, float *__restrict__ hS) {
     __shared__ double sd[8];
     __shared__ float sf[8];
     __shared__ int si[8];
@@ -58,6 +59,11 @@ __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict_
         float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + tid * 2;
         hr[0] = v0; hr[1] = v1;
     }
+    if (hS) {      // thread tid holds step i = tid of all eight lanes j: granule (i / 4, j), slot i % 4
+        float *d = hS + (size_t)b * HID + (tid >> 2) * 32 + (tid & 3);
+#pragma unroll
+        for (int j = 0; j < 8; j++) d[j * 4] = v[j];
+    }
     float mx = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
@@ -82,7 +88,11 @@ __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict_
 }
 extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum); g_launches++;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL); g_launches++;
+}
+extern "C" void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, int nb) {
+    if (nb <= 0) return;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, hS); g_launches++;
 }
 
 // (Router logits live in k_router_tile.cu.)
@@ -234,58 +244,64 @@ __global__ void __launch_bounds__(128) group_place_kernel(const unsigned *__rest
 #pragma unroll
     for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = sl[k];
 }
-// Decode batches (up to 256 tokens = 2048 pairs): the whole grouping in one CTA, so that the step costs one launch instead of
-// five, and without a serial walk: every pair sets its token's bit in its expert's row of a shared-memory bit table; an expert's
+// Decode batches (up to 256 tokens = 2048 pairs): the whole grouping in one CTA, so that the step costs one launch instead of five, and without a
+// serial walk: every pair sets its token's bit in its expert's row of a shared-memory bit table; an expert's
 // count is the population of its row, a pair's place inside its expert the population below its token's bit, which is the
 // reference's order (pairs of an expert in token order).  The scan over experts and the per-token sort of the eight pair slots
 // follow in the same CTA.
+// MAXTOK tokens at most, NT threads (the first 256 own one expert each).  Used up to 256 tokens; a 2048-token instance (160 KB of
+// shared memory, 1024 threads) works but one SM takes longer over 16,384 pairs than the three kernels of the general path below.
 #define GS_MAXTOK 256
-#define GS_WORDS (GS_MAXTOK / 32)
-__global__ void __launch_bounds__(NEXP) group_small_kernel(GroupArgs g) {
-    __shared__ unsigned s_mask[NEXP][GS_WORDS];
+template <int MAXTOK, int NT>
+__global__ void __launch_bounds__(NT) group_cta_kernel(GroupArgs g) {
+    constexpr int WORDS = MAXTOK / 32;
+    extern __shared__ __align__(16) unsigned gs_smem[];
+    unsigned (*s_mask)[WORDS] = reinterpret_cast<unsigned (*)[WORDS]>(gs_smem);                         // [NEXP][WORDS]
+    int *s_slot = reinterpret_cast<int *>(gs_smem + NEXP * WORDS);                                        // [MAXTOK * TOPK]
+    unsigned short (*s_wpre)[WORDS] = reinterpret_cast<unsigned short (*)[WORDS]>(s_slot + MAXTOK * TOPK); // [NEXP][WORDS] pairs before word w
     __shared__ int s_start[NEXP];
-    __shared__ int s_slot[GS_MAXTOK * TOPK];
     __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
-    const int e = threadIdx.x, lane = e & 31, wid = e >> 5, nb = g.nb, np = nb * TOPK;
-#pragma unroll
-    for (int w = 0; w < GS_WORDS; w++) s_mask[e][w] = 0u;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nb = g.nb, np = nb * TOPK;
+    for (int i = tid; i < NEXP * WORDS; i += NT) gs_smem[i] = 0u;
     __syncthreads();
-    for (int i = e; i < np; i += NEXP) { const int t = i >> 3; atomicOr(&s_mask[g.top[i]][t >> 5], 1u << (t & 31)); }
+    for (int i = tid; i < np; i += NT) { const int t = i >> 3; atomicOr(&s_mask[g.top[i]][t >> 5], 1u << (t & 31)); }
     __syncthreads();
-    int cnt = 0;
+    if (tid < NEXP) {
+        const int e = tid;
+        int cnt = 0;
+#pragma unroll 8
+        for (int w = 0; w < WORDS; w++) { s_wpre[e][w] = (unsigned short)cnt; cnt += __popc(s_mask[e][w]); }
+        if (g.ecnt) g.ecnt[e] = cnt;
+        const int used = cnt > 0, na = (cnt + g.tn_a - 1) / g.tn_a, nb_ = (cnt + g.tn_b - 1) / g.tn_b;
+        int c = cnt, u = used, a = na, b = nb_;
 #pragma unroll
-    for (int w = 0; w < GS_WORDS; w++) cnt += __popc(s_mask[e][w]);
-    if (g.ecnt) g.ecnt[e] = cnt;
-    const int used = cnt > 0, na = (cnt + g.tn_a - 1) / g.tn_a, nb_ = (cnt + g.tn_b - 1) / g.tn_b;
-    int c = cnt, u = used, a = na, b = nb_;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        int tc = __shfl_up_sync(0xffffffffu, c, o), tu = __shfl_up_sync(0xffffffffu, u, o);
-        int t1 = __shfl_up_sync(0xffffffffu, a, o), t2 = __shfl_up_sync(0xffffffffu, b, o);
-        if (lane >= o) { c += tc; u += tu; a += t1; b += t2; }
+        for (int o = 1; o < 32; o <<= 1) {
+            int tc = __shfl_up_sync(0xffffffffu, c, o), tu = __shfl_up_sync(0xffffffffu, u, o);
+            int t1 = __shfl_up_sync(0xffffffffu, a, o), t2 = __shfl_up_sync(0xffffffffu, b, o);
+            if (lane >= o) { c += tc; u += tu; a += t1; b += t2; }
+        }
+        if (lane == 31) { w_cnt[wid] = c; w_used[wid] = u; w_ta[wid] = a; w_tb[wid] = b; }
+        asm volatile("bar.sync 1, 256;" ::: "memory");                   // the eight warps that own experts
+        int oc = 0, ou = 0, oa = 0, ob = 0;
+        for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
+        const int start = oc + c - cnt, uidx = ou + u - used, ta0 = oa + a - na, tb0 = ob + b - nb_;
+        g.estart[e] = used ? start : -1;
+        s_start[e] = start;
+        if (used) {
+            g.ue[uidx] = e; g.ustart[uidx] = start;
+            for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * g.tn_a, min(g.tn_a, cnt - t * g.tn_a), e}; g.tiles_a[ta0 + t] = m; }
+            for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * g.tn_b, min(g.tn_b, cnt - t * g.tn_b), e}; g.tiles_b[tb0 + t] = m; }
+        }
+        if (e == NEXP - 1) { const int nu = uidx + used; *g.nu = nu; g.ustart[nu] = start + cnt; *g.ntiles_a = ta0 + na; *g.ntiles_b = tb0 + nb_; }
     }
-    if (lane == 31) { w_cnt[wid] = c; w_used[wid] = u; w_ta[wid] = a; w_tb[wid] = b; }
     __syncthreads();
-    int oc = 0, ou = 0, oa = 0, ob = 0;
-    for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
-    const int start = oc + c - cnt, uidx = ou + u - used, ta0 = oa + a - na, tb0 = ob + b - nb_;
-    g.estart[e] = used ? start : -1;
-    s_start[e] = start;
-    if (used) {
-        g.ue[uidx] = e; g.ustart[uidx] = start;
-        for (int t = 0; t < na; t++) { MoeTile m = {uidx, start + t * g.tn_a, min(g.tn_a, cnt - t * g.tn_a), e}; g.tiles_a[ta0 + t] = m; }
-        for (int t = 0; t < nb_; t++) { MoeTile m = {uidx, start + t * g.tn_b, min(g.tn_b, cnt - t * g.tn_b), e}; g.tiles_b[tb0 + t] = m; }
-    }
-    if (e == NEXP - 1) { const int nu = uidx + used; *g.nu = nu; g.ustart[nu] = start + cnt; *g.ntiles_a = ta0 + na; *g.ntiles_b = tb0 + nb_; }
-    __syncthreads();
-    for (int i = e; i < np; i += NEXP) {                             // every pair finds its place
+    for (int i = tid; i < np; i += NT) {                             // every pair finds its place
         const int x = g.top[i], t = i >> 3, w = t >> 5;
-        int r = s_start[x] + __popc(s_mask[x][w] & ((1u << (t & 31)) - 1u));
-        for (int v = 0; v < w; v++) r += __popc(s_mask[x][v]);
+        const int r = s_start[x] + s_wpre[x][w] + __popc(s_mask[x][w] & ((1u << (t & 31)) - 1u));
         g.utok[r] = t; g.uw[r] = g.topw[i]; if (g.uexp) g.uexp[r] = x; s_slot[i] = r;
     }
     __syncthreads();
-    for (int t = e; t < nb; t += NEXP) {                             // tp: the token's eight slots ascending
+    for (int t = tid; t < nb; t += NT) {                             // tp: the token's eight slots ascending
         int sl[TOPK];
 #pragma unroll
         for (int k = 0; k < TOPK; k++) { sl[k] = s_slot[t * TOPK + k]; g.slot[t * TOPK + k] = sl[k]; }
@@ -297,9 +313,16 @@ __global__ void __launch_bounds__(NEXP) group_small_kernel(GroupArgs g) {
         for (int k = 0; k < TOPK; k++) g.tp[t * TOPK + k] = sl[k];
     }
 }
+template <int MAXTOK, int NT>
+static void launch_group_cta(cudaStream_t st, const GroupArgs *g) {
+    const int smem = NEXP * (MAXTOK / 32) * 4 + MAXTOK * TOPK * 4 + NEXP * (MAXTOK / 32) * 2;
+    static bool attr_done = false;
+    if (!attr_done) { cudaFuncSetAttribute(group_cta_kernel<MAXTOK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_done = true; }
+    group_cta_kernel<MAXTOK, NT><<<1, NT, smem, st>>>(*g);
+}
 extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
-    if (g->nb <= GS_MAXTOK) { group_small_kernel<<<1, NEXP, 0, st>>>(*g); g_launches++; return; }
+    if (g->nb <= 256) { launch_group_cta<256, 256>(st, g); g_launches++; return; }
     const int np = g->nb * TOPK;
     cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit rows + the 256 counters behind them
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);

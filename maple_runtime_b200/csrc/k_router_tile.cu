@@ -265,11 +265,11 @@ extern "C" void k_router_pack_small(cudaStream_t st, const uint16_t *router, voi
     router_pack_w_small_kernel<<<NEXP * HID / 4 / 256, 256, 0, st>>>(router, (uint2 *)router_s);
     k_count_add(1);
 }
-extern "C" void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, const float *bias, float *logits, int nb, int *err) {
+extern "C" void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, int relaid, const float *bias, float *logits, int nb, int *err) {
     if (nb <= 0) return;
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB); attr_done = true; }
-    router_pack_h_small_kernel<<<nb * 2, 256, 0, st>>>(hn, (float4 *)hS, nb);
+    if (!relaid) router_pack_h_small_kernel<<<nb * 2, 256, 0, st>>>(hn, (float4 *)hS, nb);
     router_small_kernel<<<dim3(NEXP / RS_EXP, (nb + RS_TOK - 1) / RS_TOK), 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
-    k_count_add(2);
+    k_count_add(relaid ? 1 : 2);
 }

@@ -46,12 +46,14 @@ typedef struct {
 void k_count_reset(void); long k_count(void);
 
 void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb);
+/* the same, and the normalised rows once more in the decode router's layout (hS, nb*HID*4 bytes): k_router_logits_small then takes relaid = 1 */
+void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, int nb);
 /* prefill-sized batches: router_t = the layer's router rows re-laid by k_router_pack (NEXP*HID*2 bytes), hT = scratch of
  * ceil(nb/16)*16*HID*8 bytes; err receives 31 if a bounded wait inside the kernel ran out */
 void k_router_pack(cudaStream_t st, const uint16_t *router, void *router_t);
 /* decode batches: router_s = the rows re-laid by k_router_pack_small (NEXP*HID*2 bytes), hS = scratch of nb*HID*4 bytes */
 void k_router_pack_small(cudaStream_t st, const uint16_t *router, void *router_s);
-void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, const float *bias, float *logits, int nb, int *err);
+void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, int relaid, const float *bias, float *logits, int nb, int *err);
 void k_router_logits_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err);
 void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb);
 typedef struct {
