@@ -61,6 +61,8 @@ int gmoe_forward_chunk(int chunk, int nb, int l0, int nl, const float *bias);
 /* The layer loop of gmoe_forward* is replayed as a CUDA graph from the second call with the same (nb, l0, nl) on (one launch per
  * call).  on = 0 switches that off (also: environment GMOE_GRAPH=0), e.g. to time every stage with gmoe_profile. */
 int gmoe_set_graph(int on);
+/* How many times a captured layer loop has been replayed since load (tests use it to know that a call was a replay). */
+long gmoe_graph_launches(void);
 /* Waits for the stream; returns the GPU seconds between the last gmoe_forward_dev's first and last kernel. */
 double gmoe_sync(void);
 /* rmsnorm(post_ln[L]) of the device-resident hidden state + int8 + router logits: the part of gfull_attn
@@ -98,6 +100,9 @@ int gmoe_stage(const char *name, int L, int nb);
 /* 0 = grouped kernels chosen by size (default), 1 = force the mma.sync register-decode kernels,
  * 2 = force the tcgen05 kernels. */
 int gmoe_set_path(int path);
+/* The exact-order router kernel for batches above 256 tokens gives each thread tt tokens x 16 experts; tt = 4..8 pins that
+ * (every value gives the same bits), 0 = choose by batch size (default). */
+void gmoe_router_tile_tokens(int tt);
 /* Copies bytes [off, off+bytes) of a registered region (gpre_region id, or the id a synthetic layer got: regions are
  * numbered in registration order) back to the host, to check what lives in HBM. */
 int gmoe_region_read(int region, size_t off, void *dst, size_t bytes);

@@ -20,7 +20,7 @@ void k_count_add(long n);
 #define NEXP 256
 #define TOPK 8
 #define FFN 512
-#define MAXREG 64          /* gpu_pre.m:21 */
+#define MAXREG 256         /* gpu_pre.m:21 has 64; synthetic layers that are generated again take new ids */
 #define MAXSYNTH 64
 #define MAP_CACHE 16384
 #define UMMA_TN 128        /* tokens per tile of the tcgen05 kernels (k_expert_umma.cu) */
@@ -38,7 +38,9 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; void *router_t, *router_s; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set; } LayerDev;
+typedef struct { uint16_t *router, *post_ln; void *router_t, *router_s; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set;
+                 int e0, ne;            /* the experts this GPU holds for the layer (all 256, or one rank's shard) */
+                 int synth_region;      /* region index + 1 of a synthetic layer's weights, released when the layer is replaced */ } LayerDev;
 
 static struct {
     int ready, maxtok, maxp, mask_words, keep, path, nb_cur, ep_on;
@@ -209,6 +211,8 @@ static int resolve(const char *who, const uint32_t *loc12, const int *regs, Expe
 }
 
 /* ---- layers ---------------------------------------------------------------------------------------------------- */
+static void graphs_drop(void);
+static void ep_forget_layer(int L);
 static int layer_bufs(const char *who, int L) {
     if (!S.ready) return fail(who, "not initialised");
     if (L < 0 || L >= GMOE_LAYERS) return fail(who, "layer %d outside 0..%d", L, GMOE_LAYERS - 1);
@@ -234,17 +238,25 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
     CU("gmoe", cudaMemcpyAsync(l->dsp, S.h_dsp, NEXP * sizeof(void *), cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaStreamSynchronize(S.st));
-    l->set = 1; return 0;
+    graphs_drop(); ep_forget_layer(L);            /* replays and the gathered down scales would still name the old weights */
+    l->e0 = 0; l->ne = NEXP; l->set = 1; return 0;
 }
 int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     if (layer_bufs("gmoe", L)) return -1;
     if (e0 < 0 || ne < 1 || e0 + ne > NEXP) return fail("gmoe", "experts %d..%d outside 0..255", e0, e0 + ne - 1);
     LayerDev *l = &S.ly[L];
     uint8_t *w = NULL; size_t len = (size_t)ne * MS_EXPERT_BYTES;
+    if (cudaStreamSynchronize(S.st) != cudaSuccess) return fail("gmoe", "synthetic layer %d: the stream reports an earlier error", L);
+    if (l->synth_region) {                         /* the layer is generated again: its old weights go, the region id stays (empty) */
+        cudaFree(S.reg[l->synth_region - 1]); S.reg[l->synth_region - 1] = NULL; S.reg_len[l->synth_region - 1] = 0; l->synth_region = 0;
+    }
+    l->set = 0;
     if (cudaMalloc((void **)&w, len) != cudaSuccess) return fail("gmoe", "no device memory for %d experts of layer %d", ne, L);
-    if (region_add("gmoe", w, len) < 0) return -1;
+    const int rid = region_add("gmoe", w, len);
+    if (rid < 0) { cudaFree(w); return -1; }
+    l->synth_region = rid + 1;
     k_synth_experts(S.st, seed, L, e0, ne, w);
-    memset(S.h_tab, 0, NEXP * sizeof(ExpertPtrs));
+    memset(S.h_tab, 0, NEXP * sizeof(ExpertPtrs)); memset(S.h_maps, 0, NEXP * sizeof(ExpertMaps));
     for (int e = e0; e < e0 + ne; e++) {
         const uint8_t *b = w + (size_t)(e - e0) * MS_EXPERT_BYTES; ExpertPtrs *t = &S.h_tab[e];
         t->gc = b; t->gs = (const float *)(b + MS_GU_CODES); t->uc = b + MS_GU_BYTES; t->us = (const float *)(b + MS_GU_BYTES + MS_GU_CODES);
@@ -266,7 +278,8 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     if (e1 || e2 || e3 || e4) return fail("gmoe", "synthetic layer %d: %s", L, cudaGetErrorString(e1 ? e1 : e2 ? e2 : e3 ? e3 : e4));
     e4 = cudaGetLastError();
     if (e4) return fail("gmoe", "synthetic layer %d: %s", L, cudaGetErrorString(e4));
-    l->set = 1; return 0;
+    graphs_drop(); ep_forget_layer(L);
+    l->e0 = e0; l->ne = ne; l->set = 1; return 0;
 }
 
 /* ---- per-stage events ------------------------------------------------------------------------------------------ */
@@ -383,10 +396,21 @@ static void run_layer(int L, int nb, int norm, const float *bias) {
     if (norm) run_combine((const float *const *)l->dsp, nb, S.x, S.x); else run_combine((const float *const *)l->dsp, nb, NULL, S.y);
     prof_end(7);
 }
+static int g_ep_call;      /* set while an expert-parallel entry point runs its checks */
+static int ep_rank_shard(int *e0, int *ne);
 static int check_call(const char *who, int L, int nb) {
     if (!S.ready) return fail(who, "not initialised");
     if (L < 0 || L >= GMOE_LAYERS || !S.ly[L].set) return fail(who, "layer %d has no weights", L);
     if (nb < 1 || nb > S.maxtok) return fail(who, "%d tokens outside 1..%d", nb, S.maxtok);
+    const LayerDev *l = &S.ly[L];
+    if (g_ep_call) {
+        int e0 = 0, ne = 0; ep_rank_shard(&e0, &ne);
+        if (l->e0 > e0 || l->e0 + l->ne < e0 + ne) return fail(who, "layer %d holds experts %d..%d, this rank needs %d..%d", L, l->e0, l->e0 + l->ne - 1, e0, e0 + ne - 1);
+    } else {
+        /* after gmoe_ep_init the work buffers are sized and filled for the expert-parallel path only */
+        if (S.ep_on) return fail(who, "expert parallelism is set up: use the gmoe_ep_* entry points");
+        if (l->e0 != 0 || l->ne != NEXP) return fail(who, "layer %d holds only experts %d..%d (an expert-parallel shard); a single-GPU call needs all %d", L, l->e0, l->e0 + l->ne - 1, NEXP);
+    }
     return 0;
 }
 static const float *bias_dev(const float *bias) {
@@ -400,6 +424,8 @@ static double finish(const char *who) {
     if (e == cudaSuccess && *S.h_err) {
         const int code = *S.h_err;
         *S.h_err = 0; cudaMemsetAsync(S.err, 0, 4, S.st);
+        /* a down pass that no combine followed leaves escape bits behind; they are only ever OR-ed into */
+        cudaMemsetAsync(S.wire, 0, WIRE_BYTES((size_t)S.maxp), S.st);
         fail(who, "a kernel gave up waiting (code %d: %s); results are invalid", code,
              code == 41 ? "a rank did not arrive at the expert-parallel rendezvous" : code == 31 ? "router operand ring" : "barrier inside an expert kernel");
         return -1.0;
@@ -419,6 +445,13 @@ static double finish(const char *who) {
 #define NGRAPH 16
 static struct { int nb, l0, nl, bias, path, prof, ep, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
 static int g_graph_on = -1;
+static long g_graph_launches;
+long gmoe_graph_launches(void) { return g_graph_launches; }
+/* forget every captured layer loop: the weights or the work buffers a replay names have changed */
+static void graphs_drop(void) {
+    if (S.st) cudaStreamSynchronize(S.st);
+    for (int i = 0; i < NGRAPH; i++) { if (GR[i].exec) cudaGraphExecDestroy(GR[i].exec); memset(&GR[i], 0, sizeof GR[i]); }
+}
 static int graphs_on(void) {
     if (g_graph_on < 0) { const char *e = getenv("GMOE_GRAPH"); g_graph_on = !(e && e[0] == '0'); }
     return g_graph_on && !S.keep;
@@ -453,6 +486,7 @@ static int layers_enqueue_ep(int nb, int l0, int nl, const float *bd, int ep) {
         if (e != cudaSuccess) { GR[k].exec = NULL; GR[k].seen = 2; cudaGetLastError(); return fail("gmoe", "graph capture of the layer loop: %s", cudaGetErrorString(e)); }
     } else k_count_add(GR[k].launches);
     CU("gmoe", cudaGraphLaunch(GR[k].exec, S.st));
+    g_graph_launches++;
     return 0;
 }
 static int layers_enqueue(int nb, int l0, int nl, const float *bd) { return layers_enqueue_ep(nb, l0, nl, bd, 0); }
@@ -530,6 +564,7 @@ int gmoe_post_norm(int L, int nb, float *logits) {
 static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc, const int *regs, const int *ustart,
                            const int *ptok, const float *pw, const int *tp) {
     if (!S.ready) return fail(who, "not initialised");
+    if (S.ep_on) return fail(who, "expert parallelism is set up: use the gmoe_ep_* entry points");
     if (nb < 1 || nb > S.maxtok) return fail(who, "%d tokens outside 1..%d", nb, S.maxtok);
     if (nu < 1 || nu > NEXP) return fail(who, "%d used experts outside 1..%d", nu, NEXP);
     int np = ustart[nu];
@@ -659,7 +694,8 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "group")) run_group(nb);
     else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 1); }
     else if (!strcmp(name, "actq")) run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 2);
-    else if (!strcmp(name, "down")) run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 4);
+    else if (!strcmp(name, "down")) { if (use_umma(nb)) cudaMemsetAsync(S.wire, 0, WIRE_BYTES((size_t)S.maxp), S.st);   /* a repeated stage must not find the previous run's escape bits */
+        run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 4); }
     else if (!strcmp(name, "combine_y")) run_combine((const float *const *)l->dsp, nb, NULL, S.y);
     else if (!strcmp(name, "combine_x")) run_combine((const float *const *)l->dsp, nb, S.x, S.x);
     else return fail("gmoe", "no stage named %s", name);
@@ -815,6 +851,12 @@ static struct {
     float *ds_all[GMOE_LAYERS]; const float **dsp[GMOE_LAYERS];   /* every expert's down scales gathered per layer, and the pointer table over them */                     /* the same tables in device memory */
 } EP;
 
+static int ep_rank_shard(int *e0, int *ne) { *e0 = EP.rank * EP.epr; *ne = EP.epr; return 0; }
+/* layer L got new weights: the down scales gathered from all ranks are stale */
+static void ep_forget_layer(int L) {
+    if (EP.ds_all[L]) { cudaFree(EP.ds_all[L]); EP.ds_all[L] = NULL; }
+    if (EP.dsp[L]) { cudaFree((void *)EP.dsp[L]); EP.dsp[L] = NULL; }
+}
 static int ep_nccl(const char *who) {
     if (EP.lib) return 0;
     EP.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
@@ -836,6 +878,7 @@ int gmoe_ep_unique_id(void *out128) {
 int gmoe_ep_init(int rank, int world, const void *id128) {
     if (!S.ready) return fail("gmoe", "gmoe_ep_init before gmoe_init");
     if (S.ep_on) return fail("gmoe", "expert parallelism is already set up");
+    graphs_drop();                              /* the buffers reallocated below are named by every captured layer loop */
     if (world < 1 || world > 8 || (NEXP % world) || rank < 0 || rank >= world) return fail("gmoe", "rank %d of %d", rank, world);
     if (ep_nccl("gmoe")) return -1;
     ncclUniqueId id; memcpy(&id, id128, sizeof id);
@@ -944,7 +987,9 @@ static int run_layer_ep(int L, int nb, const float *bias) {
  * Device-resident form (gmoe_x_upload / gmoe_x_download, gmoe_chunks_upload); asynchronous; every rank calls it with the same nb. */
 int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
     if (!S.ep_on) return fail("gmoe", "expert parallelism is not set up");
-    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) return -1;
+    g_ep_call = 1;
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) { g_ep_call = 0; return -1; }
+    g_ep_call = 0;
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     if (chunk >= 0) {
@@ -958,7 +1003,9 @@ int gmoe_ep_forward_dev(int chunk, int nb, int l0, int nl, const float *bias) {
 /* Host in/out, like gmoe_forward. */
 double gmoe_ep_forward(float *x, int nb, int l0, int nl, const float *bias) {
     if (!S.ep_on) { fail("gmoe", "expert parallelism is not set up"); return -1.0; }
-    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) return -1.0;
+    g_ep_call = 1;
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || ep_layer_scales(L)) { g_ep_call = 0; return -1.0; }
+    g_ep_call = 0;
     const float *bd = bias_dev(bias);
     cudaEventRecord(S.e0, S.st);
     CUD("gmoe", cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));

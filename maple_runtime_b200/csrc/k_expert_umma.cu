@@ -61,13 +61,6 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-#ifdef UMMA_TRACE
-// timing build: every bounded wait adds its duration to a per-warp register counter; CTA 0 stores them at the end
-__device__ long long g_um_trace[32][8];
-#define TWAIT(id, call) ([&]() { long long t_ = clock64(); bool ok_ = (call); wacc[id] += clock64() - t_; return ok_; }())
-#else
-#define TWAIT(id, call) (call)
-#endif
 template <int KB, int MODE>
 __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const __grid_constant__ TMap4 bmap) {
     extern __shared__ __align__(1024) uint8_t um_smem_raw[];
@@ -97,9 +90,6 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     tc_fence_after();
     const uint32_t tb = sh->tmem_base;
     bool live = true;
-#ifdef UMMA_TRACE
-    long long wacc[4] = {0, 0, 0, 0}; const long long t_begin = clock64();
-#endif
 
     if (warp < 8) {
         // ---------------- decode: one weight row per thread, packed bytes from the shared-memory ring ----------------
@@ -110,7 +100,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
 #pragma unroll 1
             for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
                 const int ws = wcnt % UM_WSTAGES;
-                if (!TWAIT(0, mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp))) { live = false; break; }
+                if (!mbar_wait(&sh->w_full[ws], (wcnt / UM_WSTAGES) & 1, abortp)) { live = false; break; }
                 const uint8_t *wr = wsm + ws * UM_WBYTES + R * 128;
 #pragma unroll
                 for (int rd = 0; rd < 2; rd++, acnt++) {                 // two rounds per weight stage, two 128-column blocks per round
@@ -126,7 +116,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                             for (int j = 0; j < 8; j++) o[sft * 8 + j] = (w[j] >> (2 * sft)) & 0x03030303u;
                     };
                     decode(2 * rd, r); decode(2 * rd + 1, r2);            // both blocks are ready before the stage is free
-                    if (!TWAIT(1, mbar_wait(&sh->a_empty[h][as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp))) { live = false; break; }
+                    if (!mbar_wait(&sh->a_empty[h][as], ((acnt / UM_ASTAGES) & 1) ^ 1, abortp)) { live = false; break; }
                     tc_fence_after();
                     tmem_st32(a_lane + as * 128, r);
                     tmem_st32(a_lane + as * 128 + 32, r2);
@@ -151,7 +141,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 const ExpertMaps *em = a.maps + tile.ex;
                 for (int sb = 0; sb < NSB && live; sb++, wcnt++) {
                     const int ws = wcnt % UM_WSTAGES;
-                    if (!TWAIT(0, mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
+                    if (!mbar_wait(&sh->w_empty[ws], ((wcnt / UM_WSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
                     const uint32_t dst = smem_u32(wsm + ws * UM_WBYTES);
                     mbar_expect_tx(&sh->w_full[ws], UM_WBYTES);
                     if (GATEUP) {
@@ -174,7 +164,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
                 for (int kb = 0; kb < KB && live; kb += 2, bcnt++) {
                     const int s = bcnt % UM_BSTAGES;
-                    if (!TWAIT(0, mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp))) { live = false; break; }
+                    if (!mbar_wait(&sh->b_empty[s], ((bcnt / UM_BSTAGES) & 1) ^ 1, abortp)) { live = false; break; }
                     // only as many rows as the tile has pairs, in steps of 32 (the MMA reads (cnt + 15) & ~15 <= that many)
                     const int bi = tile.cnt > 0 ? (tile.cnt - 1) >> 5 : 0;
                     mbar_expect_tx(&sh->b_full[s], 2 * 128 * 32 * (bi + 1));
@@ -197,12 +187,12 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 const MoeTile tile = tnext;
                 if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
                 const uint32_t idesc = idesc_i8_u8s8((uint32_t)((tile.cnt + 15) & ~15));
-                if (!TWAIT(0, mbar_wait(&sh->acc_empty, (icnt & 1) ^ 1, abortp))) { live = false; break; }
+                if (!mbar_wait(&sh->acc_empty, (icnt & 1) ^ 1, abortp)) { live = false; break; }
                 tc_fence_after();
                 const uint32_t d = tb + h * 128;
 #pragma unroll 1
                 for (int kb = 0; kb < KB; kb += 2) {
-                    if (!TWAIT(1, mbar_wait_addr(afull0 + as * 8, ap, abortp)) || !TWAIT(2, mbar_wait_addr(bfull0 + bs * 8, bp, abortp))) { live = false; break; }
+                    if (!mbar_wait_addr(afull0 + as * 8, ap, abortp) || !mbar_wait_addr(bfull0 + bs * 8, bp, abortp)) { live = false; break; }
                     tc_fence_after();
                     const uint32_t acol = tb + UM_ACOL + as * 128 + h * 64;
                     const uint64_t bd = bdesc0 + (uint64_t)(bs * (UM_BBYTES >> 4));
@@ -238,9 +228,6 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             t1 = t2; ep1 = a.tab[t1.ex];
             if (item + 2 * stride < nitems) t2 = a.tiles[(item + 2 * stride) / MB];
             const int mb = item % MB, cnt = tile.cnt, N = (cnt + 15) & ~15;
-#ifdef UMMA_TRACE
-            long long tq0 = clock64();
-#endif
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + 2 * row;      // down: accumulator 0 holds row r0, accumulator 1 row r0 + 1
             const float s0 = GATEUP ? ep.gs[r0] : (DENSE ? ep.ds[r0] : 0.0f), s1 = GATEUP ? ep.us[r0] : (DENSE ? ep.ds[r0 + 1] : 0.0f);
             __syncwarp();
@@ -250,24 +237,15 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                 if (MODE == 1 && a.rx_src) { const int2 sp = a.rx_src[pair]; sh->m_dst[ew][n] = (unsigned long long)(uintptr_t)(a.peer_wire[sp.x] + (size_t)sp.y * WIRE_PITCH); }
             }
             __syncwarp();
-#ifdef UMMA_TRACE
-            wacc[1] += clock64() - tq0;
-#endif
-            if (!TWAIT(0, mbar_wait(&sh->acc_full, icnt & 1, abortp))) { live = false; break; }
+            if (!mbar_wait(&sh->acc_full, icnt & 1, abortp)) { live = false; break; }
             tc_fence_after();
             const uint32_t d_lane = tb + ((uint32_t)(q4 * 32) << 16);
             const int c_last = ((N / 16 - 1 - half) & ~1) + half;           // this warp's last piece (negative: none)
             if (half * 16 >= N) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->acc_empty); }
             for (int c0 = half * 16; c0 < N; c0 += 32) {
                 uint32_t v0[16], v1[16];
-#ifdef UMMA_TRACE
-                long long tq1 = clock64();
-#endif
                 tmem_ld16(d_lane + c0, v0); tmem_ld16(d_lane + 128 + c0, v1);
                 tmem_ld_wait();
-#ifdef UMMA_TRACE
-                wacc[2] += clock64() - tq1; tq1 = clock64();
-#endif
                 if (c0 == c_last * 16) {   // the buffer is in registers: hand it back before the arithmetic
                     tc_fence_before();
                     __syncwarp();
@@ -375,15 +353,9 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                         for (int j = 0; j < 16; j++) if (j < lim) *reinterpret_cast<int2 *>(ip + j * 2048) = make_int2((int)v0[j] - 32768, (int)v1[j] - 32768);
                     }
                 }
-#ifdef UMMA_TRACE
-                wacc[3] += clock64() - tq1;
-#endif
             }
         }
     }
-#ifdef UMMA_TRACE
-    if (blockIdx.x == 0 && lane == 0) { for (int i = 0; i < 4; i++) g_um_trace[warp][i] = wacc[i]; g_um_trace[warp][4] = clock64() - t_begin; }
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 10) {
@@ -427,7 +399,3 @@ extern "C" void k_gather_rows(cudaStream_t st, const int8_t *src, const int *row
     gather_rows_kernel<<<(np + 7) / 8, 256, 0, st>>>(src, rows, dst, np);
     k_count_add(1);
 }
-#ifdef UMMA_TRACE
-extern "C" void k_umma_trace_reset(void) {}
-extern "C" void k_umma_trace_dump(long long *host, int *n) { (void)n; cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_um_trace, sizeof(long long) * 32 * 8); }
-#endif

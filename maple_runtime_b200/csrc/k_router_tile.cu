@@ -163,8 +163,8 @@ extern "C" void k_router_pack(cudaStream_t st, const uint16_t *router, void *rou
     k_count_add(1);
 }
 static int g_force_tt = 0;
-// tests: pin the tokens per thread (4..8; 0 = choose by batch size)
-extern "C" void k_router_tile_force(int tt) { g_force_tt = (tt >= 4 && tt <= 8) ? tt : 0; }
+// pins the tokens per thread (4..8; 0 = choose by batch size); include/gmoe.h
+extern "C" void gmoe_router_tile_tokens(int tt) { g_force_tt = (tt >= 4 && tt <= 8) ? tt : 0; }
 template <int TT>
 static void launch_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err) {
     static bool attr_done = false;

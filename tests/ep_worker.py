@@ -69,13 +69,16 @@ def main():
             want, _ = o.moe(ml.synth_router(clib, SEED, L), ml.synth_norm(clib, SEED, L), ml.synth_experts(clib, SEED, L, 0, 256), want, 1, bias, dump=False)
         for path in (1, 2):
             g.set_path(path)
-            got = x.copy()
-            secs = clib.gmoe_ep_forward(got.ctypes.data, nb, 0, layers, None if bias is None else bias.ctypes.data)
-            assert secs > 0, g.err()
-            same = np.array_equal(got.view(np.uint32), want.view(np.uint32))
-            rel = float(np.abs(got - want).max() / np.abs(want).max())
-            print(f"rank {rank} path {path}: received {clib.gmoe_ep_received()} pairs in the last layer, equal bits {same}, rel {rel:.2e}", flush=True)
-            assert same, f"rank {rank} path {path}: rel {rel:.3e}"
+            replays = clib.gmoe_graph_launches()
+            for call in range(3):       # the first call runs plain launches, the second captures the layer loop, the third replays it
+                got = x.copy()
+                secs = clib.gmoe_ep_forward(got.ctypes.data, nb, 0, layers, None if bias is None else bias.ctypes.data)
+                assert secs > 0, g.err()
+                same = np.array_equal(got.view(np.uint32), want.view(np.uint32))
+                rel = float(np.abs(got - want).max() / np.abs(want).max())
+                print(f"rank {rank} path {path} call {call}: received {clib.gmoe_ep_received()} pairs in the last layer, equal bits {same}, rel {rel:.2e}", flush=True)
+                assert same, f"rank {rank} path {path} call {call}: rel {rel:.3e}"
+            assert clib.gmoe_graph_launches() - replays >= 2, "the expert-parallel layer loop was not replayed as a graph"
     dist.barrier()
     dist.destroy_process_group()
 

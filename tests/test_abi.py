@@ -57,12 +57,15 @@ def test_argument_checks_before_any_device_work(clib):
     assert clib.gpre_init(0, 8) == -1 and clib.gpre_init(1 << 20, 8) == -1
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/maple.c"), reason="reference sources not on this machine")
+MAPLE_C = os.environ.get("MAPLE_C", "/root/reference/maple.c")   # the reference's single source file, where this machine keeps it
+
+
+@pytest.mark.skipif(not os.path.exists(MAPLE_C), reason="reference sources not on this machine")
 def test_reference_links_against_the_library(tmp_path):
     """maple.c built with -DGPU_HEAD resolves every plug-in symbol from libgpre_cuda.so (link check only)."""
     from maple_runtime_b200 import lib as ml
     exe = tmp_path / "maple_gpu"
-    r = subprocess.run(["gcc", "-w", "-O1", "-march=x86-64-v3", "-DGPU_HEAD", "-o", str(exe), "/root/reference/maple.c",
+    r = subprocess.run(["gcc", "-w", "-O1", "-march=x86-64-v3", "-DGPU_HEAD", "-o", str(exe), MAPLE_C,
                         ml.LIB_PATH, "-lpthread", "-lm", "-Wl,-rpath," + os.path.dirname(ml.LIB_PATH)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
 

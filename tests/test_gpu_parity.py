@@ -89,7 +89,7 @@ def test_tiled_router_equals_oracle_for_every_tile_size(nb, tt, layers, clib, or
     hn = weights.hidden(400 + tt, nb)
     bias = np.linspace(-1.0, 1.0, 256).astype(np.float32)
     want = oracle.router_logits(router, hn)
-    clib.k_router_tile_force(tt)
+    clib.gmoe_router_tile_tokens(tt)
     try:
         g.poke("hn", hn)
         g.stage("router", 2, nb)
@@ -98,7 +98,7 @@ def test_tiled_router_equals_oracle_for_every_tile_size(nb, tt, layers, clib, or
         g.stage("router_bias", 2, nb)
         assert same_bits(g.peek("logits", nb).reshape(nb, 256), want + bias[None, :])
     finally:
-        clib.k_router_tile_force(0)
+        clib.gmoe_router_tile_tokens(0)
 
 
 def test_compact_down_rows_escape_plane(layers, clib, oracle, weights):

@@ -1,0 +1,64 @@
+"""The path the benchmark times, compared with the reference itself: gmoe_forward with stages NOT kept, so that the
+layer loop is captured as a CUDA graph on the second call with a key and replayed from then on (the kernels also take
+their lean variants: no stored dot products, no fp32 copies of the compact down rows).  Every call's hidden state
+must have the bits of maple.c's CPU path (oracle/_ref, rh_stack = the MoE half of step_batch, maple.c:732-835)."""
+import numpy as np
+import pytest
+
+from conftest import SEED, same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def lean(gpu):
+    """The session's library instance with stage keeping off and graph replay on; restored afterwards."""
+    gpu.keep_stages(False)
+    gpu.lib.gmoe_set_graph(1)
+    yield gpu
+    gpu.keep_stages(True)
+
+
+@pytest.mark.parametrize("nb,nl,stream", [(2048, 3, 910), (64, 3, 911), (700, 2, 912), (1, 2, 913)])
+def test_graph_replay_has_the_reference_bits(nb, nl, stream, lean, reference, weights):
+    g = lean
+    for L in range(nl):
+        g.synth_layer(SEED + 5, L)
+        reference.set_layer(L, *weights.layer(L, SEED + 5))
+    x = weights.hidden(stream, nb)
+    want = x.copy()
+    assert reference.stack(want, 0, nl) >= 0
+    before = g.lib.gmoe_graph_launches()
+    for call in range(4):                      # 1: plain launches, 2: capture + first replay, 3 and 4: replays
+        got = x.copy()
+        g.forward(got, 0, nl)
+        assert same_bits(got, want), f"call {call}: rel {np.abs(got - want).max() / np.abs(want).max():.3e}"
+    assert g.lib.gmoe_graph_launches() - before >= 3
+    # a different chunk through the same captured graph
+    x2 = weights.hidden(stream + 50, nb)
+    want2 = x2.copy(); reference.stack(want2, 0, nl)
+    got2 = x2.copy(); g.forward(got2, 0, nl)
+    assert same_bits(got2, want2)
+    # put back the layers the other modules expect
+    for L in range(nl):
+        g.synth_layer(SEED, L)
+
+
+def test_replay_of_the_device_resident_form(lean, reference, weights):
+    """gmoe_forward_chunk (the benchmark's `value` leg): chunks kept in HBM, asynchronous calls, one sync per step."""
+    g, nb, nl = lean, 2048, 2
+    for L in range(nl):
+        g.synth_layer(SEED + 6, L)
+        reference.set_layer(L, *weights.layer(L, SEED + 6))
+    chunks = np.concatenate([weights.hidden(930 + c, nb) for c in range(2)])
+    g._chk(g.lib.gmoe_chunks_upload(chunks.ctypes.data, nb, 2))
+    for step in range(5):
+        c = step % 2
+        g._chk(g.lib.gmoe_forward_chunk(c, nb, 0, nl, None))
+        assert g._chk(g.lib.gmoe_sync()) > 0
+        got = np.empty((nb, 2048), np.float32)
+        g._chk(g.lib.gmoe_x_download(got.ctypes.data, nb))
+        want = chunks[c * nb:(c + 1) * nb].copy(); reference.stack(want, 0, nl)
+        assert same_bits(got, want), f"step {step}"
+    for L in range(nl):
+        g.synth_layer(SEED, L)
