@@ -23,7 +23,6 @@ void k_count_add(long n);
 #define MAXREG 256         /* gpu_pre.m:21 has 64; synthetic layers that are generated again take new ids */
 #define MAXSYNTH 64
 #define MAP_CACHE 16384
-#define UMMA_TN 128        /* tokens per tile of the tcgen05 kernels (k_expert_umma.cu) */
 
 static char g_err[512];
 static int fail(const char *who, const char *fmt, ...) {

@@ -78,14 +78,15 @@ void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 void k_dense_mma(cudaStream_t st, const ExpertArgs *a, int rows);
 void k_down_mma(cudaStream_t st, const ExpertArgs *a, int tn);
 
-/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to 128 tokens, codes decoded in registers into tensor memory */
+/* tcgen05 kind::i8 grouped kernels (prefill): tiles of up to UMMA_TN tokens, codes decoded in registers into tensor memory */
+#define UMMA_TN 96
 /* bmap: tensor maps over the B operand rows in pair order: [pairs][2048] int8 (gate+up) or [pairs][512] int8 (down); m[i] has a box
- * of 128 bytes x 32 (i + 1) rows, so that a tile of few pairs does not pull the next experts' rows through the memory system */
+ * of 128 bytes x 32 (i + 1) rows (the kernels use i = 0..2), so that a tile of few pairs does not pull the next experts' rows through the memory system */
 typedef struct { TMap m[4]; } TMap4;
 void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* a dense matrix (rows a multiple of 256, 2048 columns) on the same kernel: maps[ex].down = its 3-D map (even / odd rows), tab[ex].ds = row
- * scales, bmap over the tokens' int8 rows, tiles of up to 128 tokens; fp32 results to down[token * down_stride + row] */
+ * scales, bmap over the tokens' int8 rows, tiles of up to UMMA_TN tokens; fp32 results to down[token * down_stride + row] */
 void k_dense_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);

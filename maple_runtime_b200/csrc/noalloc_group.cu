@@ -65,7 +65,7 @@ extern "C" int gmoe_group_noalloc(const int *top, const float *topw, int nb, int
     g.mask = s->mask; g.mask_words = (nb + 31) / 32;
     g.nu = nu; g.ue = ue; g.estart = s->estart; g.ustart = ustart; g.utok = utok; g.slot = s->slot; g.tp = tp; g.uw = uw;
     g.ecnt = NULL; g.uexp = NULL;
-    g.tiles_a = s->tiles_a; g.tiles_b = s->tiles_b; g.ntiles_a = s->ntiles_a; g.ntiles_b = s->ntiles_b; g.tn_a = 8; g.tn_b = 128;
+    g.tiles_a = s->tiles_a; g.tiles_b = s->tiles_b; g.ntiles_a = s->ntiles_a; g.ntiles_b = s->ntiles_b; g.tn_a = 8; g.tn_b = UMMA_TN;
     k_group(static_cast<cudaStream_t>(stream), &g);   // above 256 tokens: clears the masks and counters (cudaMemsetAsync), then three kernels; up to 256: one kernel with its masks in shared memory; no allocation either way
     e = cudaGetLastError();
     if (e != cudaSuccess) { fprintf(stderr, "gmoe: gmoe_group_noalloc: launch failed: %s\n", cudaGetErrorString(e)); return -3; }

@@ -38,6 +38,14 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity, vo
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort) { return mbar_wait_addr(smem_u32(bar), parity, abort); }
 
+// One lane of a fully active warp (the same one every time).  tcgen05.mma is issued by a single thread; issuing it from the elected
+// lane inside warp-uniform control flow keeps its operands in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P1;\n\telect.sync _|P1, 0xffffffff;\n\tselp.u32 %0, 1, 0, P1;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------------------
 // one warp, all lanes: allocates ncols (power of two >= 32) columns, the address lands in *dst (shared memory)
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst, uint32_t ncols) {
