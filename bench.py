@@ -7,9 +7,12 @@
 One step = one 2048-token chunk through all 24 layers on each GPU.  `value` is tokens/s with the chunk already in
 HBM (device-timed, max over ranks); `e2e` is the same through the host-buffer entry point gmoe_forward (pinned host
 input copied in, result copied out, inside the timed region).  `roofline` describes the dominant kernel (the grouped
-gate+up GEMM) from CUDA events recorded around its launches during the timed region.  `cpu_baseline` times the
-reference's own CPU code (oracle/_ref, built from maple.c) on a bounded sample on this host.  `decode` repeats the
-measurement for the 64-conversation decode shape (HBM-bound).  Prints ONE JSON line on rank 0.
+gate+up GEMM), timed with CUDA events around its launches in a pass of its own, against the tcgen05 kind::i8 rate measured
+on this GPU in the same run.  `e2e_gpre_moe` is the same chunk through 24 calls of the reference-signature gpre_moe (host
+grouping tables, host buffers: the call an unmodified maple.c makes).  `parity_check` compares two layers of the chunk with
+the reference (oracle/_ref) before anything is timed.  `cpu_baseline` times the reference's own CPU code on a bounded sample
+on this host; `--impl reference` runs that code over the whole 24-layer stack.  `decode` repeats the measurement for the
+64-conversation decode shape (HBM-bound).  Prints ONE JSON line on rank 0.
 """
 import argparse
 import json
@@ -30,8 +33,17 @@ NB, LAYERS, H = 2048, 24, 2048
 EXPERT_BYTES = 798720
 OPS_PER_PAIR = 2 * (2 * 512 * 2048 + 2048 * 512)        # int8 multiply-adds x2 of one (token, expert) pair: 6,291,456
 GU_OPS_PER_PAIR = 2 * 2 * 512 * 2048                     # the gate+up share: 4,194,304
-GU_NCU_TRAFFIC = 169.0e6 + 37.8e6                        # DRAM bytes of one gate+up launch on the 2048-token chunk (ncu, see profiles/)
 METRIC, UNIT = "moe_prefill_tokens_per_s_2048tok_chunk_24_layers", "tokens/s"
+
+
+def profiled_traffic(name):
+    """DRAM bytes per launch of a kernel as the ncu summary under profiles/ records it (a line `dram_bytes_per_launch <name>: <bytes>`)."""
+    import glob, re
+    for f in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        m = re.search(r"dram_bytes_per_launch " + re.escape(name) + r":\s*([0-9.eE+]+)", open(f).read())
+        if m:
+            return float(m.group(1)), os.path.basename(f)
+    return None, None
 
 
 def peaks():
@@ -111,49 +123,54 @@ def barrier(dist):
 
 
 # ---------------------------------------------------------------------------------------------------------------
-def cpu_reference_arm(steps, warmup, as_baseline=False, budget_s=25.0):
-    """The reference's CPU path (maple.c through oracle/_ref, documented -ffast-math build) on this host's cores.
-    A step = one 2048-token chunk through ONE of the 24 layers (a bounded sample); the 24-layer figure scales it."""
+def cpu_reference_arm(steps, warmup, nlay, budget_s=None):
+    """The reference's CPU path (maple.c through oracle/_ref, documented -ffast-math build) on this host's cores: a step = one
+    2048-token chunk through nlay distinct layers, router to combine (rh_stack).  nlay = 24 is the whole workload; a smaller nlay is
+    a bounded sample whose time is scaled to 24 layers.  budget_s stops the loop early (the baseline leg inside the GPU arm)."""
     from maple_runtime_b200 import lib as ml
     from oracle import oracle as orc
     clib = ml.load()
     cores = os.cpu_count() or 1
     kind = "reference" if orc.Reference.available(fast=True) else "port"
-    nlay = 2
     layers = [(ml.synth_router(clib, SEED, L), ml.synth_norm(clib, SEED, L), ml.synth_experts(clib, SEED, L, 0, 256)) for L in range(nlay)]
-    x = ml.synth_hidden(clib, SEED, 1000, NB)
+    x0 = ml.synth_hidden(clib, SEED, 1000, NB)
     if kind == "reference":
         ref = orc.Reference(fast=True)
         threads = ref.threads(min(cores, 64))
         for L in range(nlay):
             ref.set_layer(L, *layers[L])
-        step = lambda i: ref.stack(x, i % nlay, 1)   # noqa: E731  seconds on the reference's own clock (maple.c:47)
+
+        def step():
+            x = x0.copy(); return ref.stack(x, 0, nlay)     # seconds on the reference's own clock (maple.c:47)
     else:
         o = orc.Oracle(); threads = o.lib.orc_threads(min(cores, 64))
 
-        def step(i):
-            t = time.perf_counter(); o.moe(*layers[i % nlay], x, 1, dump=False); return time.perf_counter() - t
-    t_all = []
-    for i in range(warmup if not as_baseline else 1):
-        step(i)
-    t0 = time.perf_counter()
-    for i in range(steps):
-        t_all.append(step(i))
-        if as_baseline and time.perf_counter() - t0 > budget_s:
+        def step():
+            x = x0; t = time.perf_counter()
+            for L in range(nlay):
+                x, _ = o.moe(*layers[L], x, 1, dump=False)
+            return time.perf_counter() - t
+    for _ in range(warmup):
+        step()
+    t_all, t0 = [], time.perf_counter()
+    for _ in range(steps):
+        t_all.append(step())
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
             break
-    per_layer = sum(t_all) / len(t_all)
-    value = NB / (per_layer * LAYERS)
-    sample = f"{len(t_all)} steps of one 2048-token chunk through 1 of 24 layers each (router to combine), scaled x24"
-    return value, per_layer, {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
+    per_step = sum(t_all) / len(t_all) * (LAYERS / nlay)
+    value = NB / per_step
+    sample = (f"{len(t_all)} steps of one 2048-token chunk through {nlay} distinct layers (router to combine)" +
+              ("" if nlay == LAYERS else f", scaled x{LAYERS / nlay:g} to 24 layers"))
+    return value, per_step, len(t_all), {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
 
 
 def reference_main(args, rank, world):
     if rank != 0:
         return
-    value, per_layer, cb = cpu_reference_arm(args.steps, args.warmup)
+    value, per_step, done, cb = cpu_reference_arm(args.steps, args.warmup, LAYERS)
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_layer * LAYERS * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done, "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "config": workload_config(1), "cpu_baseline": cb,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -164,6 +181,64 @@ def workload_config(world):
             "tokens_per_step_per_gpu": NB, "layers": LAYERS,
             "parallelism": f"ep{world}: tokens split over the GPUs, {256 // world} experts per GPU, dispatch and combine by peer stores over NVLink" if world > 1 else "single",
             "l2": "inputs larger than L2: 4.9 GB of expert weights are streamed from HBM every step"}
+
+
+def parity_check(g, ml, nl):
+    """Two layers of one chunk against the reference (oracle/_ref; the CPU restatement where that is absent), layer by layer on the
+    reference's own inputs: same top-8 indices, hidden state within 1e-5 (max |d| / max |ref|, maple.c:942-946).  Runs each layer three
+    times, so that the compared result also comes from a graph replay."""
+    from oracle import oracle as orc
+    clib = g.lib
+    nlay = min(2, nl)
+    x = ml.synth_hidden(clib, SEED, 1999, NB)
+    use_ref = orc.Reference.available()
+    ref = orc.Reference() if use_ref else orc.Oracle()
+    # one thread: the reference's worker threads spin for the life of the process (maple.c:89-108) and would sit on the cores that
+    # the CPU baseline leg times later
+    worst, same_top = 0.0, True
+    for L in range(nlay):
+        lay = (ml.synth_router(clib, SEED, L), ml.synth_norm(clib, SEED, L), ml.synth_experts(clib, SEED, L, 0, 256))
+        if use_ref:
+            ref.set_layer(L, *lay); want, d = ref.moe(L, x, 1)
+        else:
+            want, d = ref.moe(*lay, x, 1)
+        for _ in range(3):
+            got = x.copy(); g.forward(got, L, 1)
+        same_top = same_top and bool(np.array_equal(g.peek("top", NB).reshape(NB, 8), d["top"]))
+        worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+        x = want
+    ok = same_top and worst <= 1e-5
+    return {"result": "equal" if ok else "DIFFERENT", "against": "oracle/_ref (maple.c compiled here)" if use_ref else "oracle port",
+            "layers": nlay, "top8_indices_equal": same_top, "hidden_max_rel": worst, "tolerance": 1e-5,
+            "how": "layer by layer on the reference's inputs, third call of each layer (a graph replay)"}
+
+
+def gpre_moe_leg(g, ml, nl, warm, steps):
+    """The chunk through nl calls of gpre_moe (gpu_pre.m:318-385; call site maple.c:763): normalised hidden rows and the grouping tables
+    come from the host, the result goes back to the host, every call synchronous.  The tables are the ones this library's own routing
+    produced for the chunk (taken layer by layer beforehand); what is timed is only the calls."""
+    clib = g.lib
+    x = ml.synth_hidden(clib, SEED, 2000, NB)
+    g._chk(clib.gmoe_x_upload(x.ctypes.data, NB))
+    calls = []
+    gloc = ml.gloc_for_contiguous()
+    for L in range(nl):
+        g._chk(clib.gmoe_forward_dev(NB, L, 1, None)); g._chk(clib.gmoe_sync())
+        nu = int(g.peek("nu", NB)[0]); ue = g.peek("ue", NB)[:nu]
+        regs = np.array([g.layer_region[L], -1, -1, -1], np.int32)
+        calls.append((g.peek("hn", NB).copy(), nu, np.ascontiguousarray(gloc[ue]), regs, g.peek("ustart", NB)[:nu + 1].copy(),
+                      g.peek("utok", NB).copy(), g.peek("uw", NB).copy(), g.peek("tp", NB).copy()))
+    t_wall, t_gpu = 0.0, 0.0
+    for i in range(warm + steps):
+        t0 = time.perf_counter(); tg = 0.0
+        for c in calls:
+            tg += g.gpre_moe(*c)[1]
+        if i >= warm:
+            t_wall += time.perf_counter() - t0; t_gpu += tg
+    return {"value": NB * steps / t_wall, "unit": UNIT, "ms_per_step": t_wall / steps * 1e3, "gpu_ms_per_step": t_gpu / steps * 1e3, "calls_per_step": nl,
+            "h2d_bytes_per_step": int(sum(c[0].nbytes + c[2].nbytes + c[4].nbytes + c[5].nbytes + c[6].nbytes + c[7].nbytes for c in calls)),
+            "d2h_bytes_per_step": NB * H * 4 * nl,
+            "note": "wall clock around the synchronous calls (pageable host arrays, as maple.c holds them); gpu_ms = the seconds the calls return"}
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -210,13 +285,15 @@ def main():
     ring = np.concatenate([ml.synth_hidden(clib, SEED, 2000 + rank * 16 + c, NB) for c in range(nring)])
     g._chk(clib.gmoe_chunks_upload(ring.ctypes.data, NB, nring))
 
-    # ---- value: chunk resident in HBM, K steps between two synchronisations, device-timed ----
+    # ---- parity on the timed path, before anything is timed ----
+    parity = parity_check(g, ml, nl) if (world == 1 and rank == 0) else "not run at N > 1 (every GPU holds a shard of the experts); tests/test_ep.py compares the expert-parallel path"
+
+    # ---- value: chunk resident in HBM, K steps, each device-timed between two events on the library's stream; graph replay, no
+    # per-stage events inside ----
     import ctypes as C
-    ev_total = []
     for i in range(warm):
         forward_chunk(i % nring); g._chk(clib.gmoe_sync())
     sampler = ClockSampler(local); sampler.start()
-    g.profile(1 << 4)                                  # events around the gate+up launches only
     l0 = clib.gmoe_launch_count()
     barrier(dist)
     t_dev = 0.0
@@ -227,11 +304,16 @@ def main():
     wall = time.perf_counter() - wall0
     barrier(dist)
     launches = clib.gmoe_launch_count() - l0
-    secs, nlaunch = g.profile_read()
-    g.profile(0)
     clocks = sampler.summary()
     t_dev = allmax(dist, t_dev)
     value = world * NB * args.steps / t_dev
+
+    # ---- the dominant kernel's own duration: a pass with events around the gate+up launches only (graph replay) ----
+    g.profile(1 << 4)                                   # one pass runs plainly, the next is captured with its event records, the rest replay it
+    for i in range(5):
+        forward_chunk(i % nring); g._chk(clib.gmoe_sync())
+    secs, nlaunch = g.profile_read()                    # the plain pass and the last replay
+    g.profile(0)
 
     # ---- stage breakdown (separate pass, all stages timed, plain launches instead of the graph replay) ----
     clib.gmoe_set_graph(0)
@@ -260,22 +342,27 @@ def main():
 
     # ---- roofline of the dominant kernel ----
     pk = peaks()
+    i8_peak = float(clib.gmoe_i8_peak(256, 30000)) if rank == 0 else 0.0      # ~40 ms of MMAs on every SM
     gu_t = float(secs[4]) / max(int(nlaunch[4]), 1)          # stage 4 is one launch per layer: the grouped gate+up GEMM
     gu_tops = GU_OPS_PER_PAIR * NB * 8 / gu_t / 1e12
-    int8_peak = 2.0 * pk["bf16_tflops_sustained"]
-    roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary)", "bound": "tensor", "achieved": gu_tops, "peak": int8_peak, "unit": "TOP/s (int8)",
-                "frac": gu_tops / int8_peak, "traffic": GU_NCU_TRAFFIC if args.layers else None, "traffic_unit": "bytes per launch",
-                "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, ncu capture summarised in profiles/prefill_2048tok_2layers_launch_list_and_top_kernels.md (169.0 MB read = weights + int8 rows once, 37.8 MB written)",
+    traffic, traffic_src = profiled_traffic("gate_up")
+    roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary, tcgen05 kind::i8)", "bound": "tensor", "achieved": gu_tops, "peak": i8_peak, "unit": "TOP/s (int8)",
+                "frac": gu_tops / i8_peak if i8_peak > 0 else None, "traffic": traffic, "traffic_unit": "bytes per launch",
+                "traffic_note": f"dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the ncu summary profiles/{traffic_src}" if traffic else "no ncu summary of this kernel under profiles/",
                 "launches_timed": int(nlaunch[4]), "avg_launch_us": gu_t * 1e6,
-                "peak_note": f"2 x the {pk['src']} sustained bf16 figure ({pk['bf16_tflops_sustained']} TF/s): no int8 figure is measured on this pool",
-                "weights_gbs": NB and 256 * 2 * 264192 / gu_t / 1e9}
+                "peak_note": "tcgen05.mma kind::i8, M=128 N=256 K=32, operands resident in shared memory, one CTA per SM, measured in this run with CUDA events (gmoe_i8_peak)",
+                "frac_of_2x_bf16_burst": gu_tops / (2.0 * pk["bf16_tflops"]), "frac_of_2x_bf16_sustained": gu_tops / (2.0 * pk["bf16_tflops_sustained"]),
+                "bf16_peaks_source": pk["src"], "weights_gbs": 256 * 2 * 264192 / gu_t / 1e9}
 
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
            "ms_per_step": t_dev / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
            "data": "synthetic", "config": workload_config(world), "clocks": clocks, "gpu_launches": int(launches),
            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": NB * H * 4, "d2h_bytes_per_step": NB * H * 4},
-           "roofline": roofline, "stage_us_per_layer": breakdown, "wall_s_timed_region": wall,
+           "roofline": roofline, "stage_us_per_layer": breakdown, "wall_s_timed_region": wall, "parity_check": parity,
            "whole_path_int8_tops": OPS_PER_PAIR * NB * 8 * nl * args.steps / t_dev / 1e12}
+    if i8_peak > 0:
+        out["whole_path_frac_of_measured_i8_peak"] = out["whole_path_int8_tops"] / world / i8_peak
+    out["whole_path_frac_of_2x_bf16_burst"] = out["whole_path_int8_tops"] / world / (2.0 * pk["bf16_tflops"])
     if args.zipf:
         out["config"]["routing"] = "router logits + per-expert bias ln(256 p_e), p_e ~ rank^-1.2 over a seeded permutation (skewed load); not the headline configuration"
     if nl != LAYERS:
@@ -285,11 +372,13 @@ def main():
     # ---- decode shape: 64 conversations x 1 token, one layer at a time over all layers (HBM-bound) ----
     if world > 1:
         out["ep_received_pairs_last_layer"] = [int(v) for v in gather_obj(dist)(clib.gmoe_ep_received())]
+    if rank == 0 and world == 1:
+        out["e2e_gpre_moe"] = gpre_moe_leg(g, ml, nl, 1, min(args.steps, 5))
     if not args.no_decode and rank == 0 and world == 1:
         out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
         out["dense_projections"] = dense_leg(g, ml, pk, warm, args.steps)
     if not args.no_cpu and rank == 0:
-        _, _, out["cpu_baseline"] = cpu_reference_arm(400, 1, as_baseline=True, budget_s=12.0)
+        _, _, _, out["cpu_baseline"] = cpu_reference_arm(400, 1, 3, budget_s=12.0)
     if rank == 0:
         print(json.dumps(out))
 
@@ -338,8 +427,8 @@ def decode_leg(g, clib, ml, nl, pk, warm, steps):
     return {"metric": "moe_decode_tokens_per_s_64_conversations", "value": nb * steps / t, "unit": UNIT,
             "ms_per_step": t / steps * 1e3, "used_experts": nu, "bytes_per_layer": layer_bytes,
             "roofline": {"kernel": "gate+up weight stream (register-decode mma.sync)", "bound": "hbm", "achieved": gu_bytes / gu_t / 1e9,
-                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_bytes / gu_t / 1e9 / pk["hbm_gbs"], "traffic": 115.9e6 + 0.3e6, "traffic_unit": "bytes per launch",
-                         "traffic_note": "ncu capture summarised in profiles/decode_64tok_top_kernels.md: every used expert's gate and up bytes once",
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_bytes / gu_t / 1e9 / pk["hbm_gbs"], "traffic": profiled_traffic("decode_gate_up")[0], "traffic_unit": "bytes per launch",
+                         "traffic_note": "from the ncu summary under profiles/ (every used expert's gate and up bytes once)",
                          "avg_launch_us": gu_t * 1e6},
             "layer_hbm_frac": layer_bytes / per_layer / 1e9 / pk["hbm_gbs"],
             "stage_us_per_layer": {name: round(float(s) / (steps * nl) * 1e6, 2) for name, s in zip(g.STAGES, secs)}}

@@ -95,8 +95,15 @@ int gmoe_poke(const char *name, const void *src, size_t bytes);
 /* keep = 1: the expert kernels also store gate, up and the int32 dot products (tot - qsum). */
 int gmoe_keep_stages(int keep);
 /* Runs one stage on the device buffers for nb tokens of layer L: "norm" (x->hn,hq..), "prep" (hn->hq..),
- * "router", "topk", "group", "gateup", "actq", "down", "combine_y" (y = sum), "combine_x" (x += sum). */
+ * "router", "router_tensor" (hn -> logits, top-8, weights on the tensor-core path), "topk", "group", "gateup", "actq", "down", "combine_y" (y = sum), "combine_x" (x += sum). */
 int gmoe_stage(const char *name, int L, int nb);
+/* Router: 0 = by size (default): batches of 512 tokens and more compute the logits on the tensor cores (fp16 x 2 terms, fp32
+ * accumulation) and recompute, in the reference's exact order of operations, every token whose nine largest logits are closer than an
+ * error bound; 1 = always the exact-order kernels (logits, weights and everything downstream have the reference's bits);
+ * 2 = tensor cores for every batch size.  In all modes the top-8 indices are the reference's (maple.c:910-923). */
+int gmoe_set_router(int mode);
+/* tokens of the last tensor-core router call that took the exact path */
+int gmoe_router_flagged(void);
 /* 0 = grouped kernels chosen by size (default), 1 = force the mma.sync register-decode kernels,
  * 2 = force the tcgen05 kernels. */
 int gmoe_set_path(int path);
@@ -139,6 +146,11 @@ int gmoe_profile_read(double *secs, long *launches);
  * kind::i8; mode 0 stages A in shared memory, mode 1 writes A to tensor memory.  Host pointers.  0 = ran,
  * -1 = bad arguments or CUDA error, -2 = the MMA never signalled completion. */
 int gmoe_umma_selftest(const uint8_t *a, const int8_t *b, int n, int kblocks, int mode, int32_t *d);
+
+/* The rate at which this GPU executes tcgen05.mma kind::i8 (M = 128, N = n, K = 32, operands resident in shared memory, one CTA per
+ * SM, iters x 4 MMAs each), timed with CUDA events: 1e12 integer operations per second, or a negative value.  The roofline
+ * denominator of the grouped expert GEMMs; n = 256 and iters >= 20000 give a run of some tens of milliseconds. */
+double gmoe_i8_peak(int n, int iters);
 
 /* ---- utilities -------------------------------------------------------------------------------------------------- */
 const char *gmoe_last_error(void);

@@ -37,7 +37,7 @@ const char *gmoe_last_error(void) { return g_err; }
 #define CU(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(who, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
 #define CUD(who, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(who, "%s: %s", #call, cudaGetErrorString(e_)); return -1.0; } } while (0)
 
-typedef struct { uint16_t *router, *post_ln; void *router_t, *router_s; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set;
+typedef struct { uint16_t *router, *post_ln; void *router_t, *router_s, *router_h; float *wnorm; TMap wmap; const float **dsp; ExpertPtrs *tab; ExpertMaps *maps; int set;
                  int e0, ne;            /* the experts this GPU holds for the layer (all 256, or one rank's shard) */
                  int synth_region;      /* region index + 1 of a synthetic layer's weights, released when the layer is replaced */ } LayerDev;
 
@@ -62,6 +62,8 @@ static struct {
     float *ring; int ring_nb, ring_n;
     unsigned prof_mask; cudaEvent_t *pev; int pev_n, pev_cap; unsigned char *pev_stage; long *pev_launch;
     int fwd_timed;
+    /* tensor-core router (k_router_umma.cu) */
+    void *hA; float *hnorm, *rpart; int *flagged, *nflagged, *rdone; TMap amap; int router_mode;
 } S;
 
 /* ------------------------------------------------------------------------------------------------------------ */
@@ -87,6 +89,15 @@ static int tmap_bytes_2d(const char *who, TMap *out, const void *base, uint64_t 
     CUresult r = g_encode((CUtensorMap *)out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(who, "cuTensorMapEncodeTiled failed (%d) for %p, %llu x %llu", (int)r, base, (unsigned long long)rows, (unsigned long long)width);
+    return 0;
+}
+/* fp16 matrix [rows][cols], row pitch in bytes; box box_cols x box_rows (box_cols * 2 = 128 bytes), 128-byte swizzle; rows past the end read as zero */
+static int tmap_f16_2d(const char *who, TMap *out, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols, uint32_t box_rows) {
+    cuuint64_t gdim[2] = {cols, rows}, gstride[1] = {pitch};
+    cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
+    CUresult r = g_encode((CUtensorMap *)out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(who, "cuTensorMapEncodeTiled failed (%d) for the fp16 matrix at %p", (int)r, base);
     return 0;
 }
 /* the down codes [2048 rows][128 bytes] seen as [1024 row pairs][2 parities][128 bytes]: a box of 128 row pairs at parity h is the
@@ -132,7 +143,10 @@ static int init_common(const char *who, int maxtok, int topk) {
     ALLOC(act, P * FFN * 4); ALLOC(gate, P * FFN * 4); ALLOC(up, P * FFN * 4); ALLOC(aq, P * FFN); ALLOC(aqs, P * 4); ALLOC(aqsum, P * 4); ALLOC(down, P * HID * 4);
     ALLOC(tab_call, NEXP * sizeof(ExpertPtrs)); ALLOC(err, 16); ALLOC(maps_call, NEXP * sizeof(ExpertMaps)); ALLOC(hq_sorted, P * HID);
     ALLOC(wire, WIRE_BYTES(P)); CU(who, cudaMemset(S.wire, 0, WIRE_BYTES(P))); ALLOC(dsp_call, NEXP * sizeof(void *));
+    ALLOC(hA, T * HID * 4); ALLOC(hnorm, T * 4); ALLOC(rpart, (size_t)8 * T * NEXP * 4); ALLOC(flagged, T * 4); ALLOC(nflagged, 16); ALLOC(rdone, T * 4); CU(who, cudaMemset(S.rdone, 0, T * 4));
+    CU(who, cudaMemset(S.hA, 0, T * HID * 4)); CU(who, cudaMemset(S.nflagged, 0, 16));
     if (tmap_init(who)) return -1;
+    if (tmap_f16_2d(who, &S.amap, S.hA, 2 * HID, T, (uint64_t)2 * HID * 2, 64, 128)) return -1;
     if (bmaps(who, P)) return -1;
     CU(who, cudaMemset(S.err, 0, 16));
     CU(who, cudaHostAlloc((void **)&S.h_err, 16, cudaHostAllocDefault)); *S.h_err = 0;
@@ -217,9 +231,10 @@ static int layer_bufs(const char *who, int L) {
     if (L < 0 || L >= GMOE_LAYERS) return fail(who, "layer %d outside 0..%d", L, GMOE_LAYERS - 1);
     LayerDev *l = &S.ly[L];
     if (!l->router) {
-        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc(&l->router_s, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->dsp, NEXP * sizeof(void *)) || dmalloc((void **)&l->post_ln, HID * 2) ||
+        if (dmalloc((void **)&l->router, (size_t)NEXP * HID * 2) || dmalloc(&l->router_t, (size_t)NEXP * HID * 2) || dmalloc(&l->router_s, (size_t)NEXP * HID * 2) || dmalloc(&l->router_h, (size_t)NEXP * HID * 2) || dmalloc((void **)&l->wnorm, 16) || dmalloc((void **)&l->dsp, NEXP * sizeof(void *)) || dmalloc((void **)&l->post_ln, HID * 2) ||
             dmalloc((void **)&l->tab, NEXP * sizeof(ExpertPtrs)) || dmalloc((void **)&l->maps, NEXP * sizeof(ExpertMaps)))
             return fail(who, "out of device memory for layer %d", L);
+        if (tmap_f16_2d(who, &l->wmap, l->router_h, HID, NEXP, (uint64_t)HID * 2, 64, 256)) return -1;
     }
     return 0;
 }
@@ -231,7 +246,7 @@ int gmoe_set_layer(int L, const uint16_t *router, const uint16_t *post_ln, const
     CU("gmoe", cudaMemcpyAsync(l->maps, S.h_maps, NEXP * sizeof(ExpertMaps), cudaMemcpyHostToDevice, S.st));
     uint16_t ones[HID]; for (int i = 0; i < HID; i++) ones[i] = 0x3F80;
     CU("gmoe", cudaMemcpyAsync(l->router, router, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st));
-    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s);
+    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s); k_router_w16(S.st, l->router, l->router_h, l->wnorm);
     CU("gmoe", cudaMemcpyAsync(l->post_ln, post_ln ? post_ln : ones, HID * 2, cudaMemcpyHostToDevice, S.st));
     CU("gmoe", cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st));
     for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
@@ -267,7 +282,7 @@ int gmoe_synth_layer(uint64_t seed, int L, int e0, int ne) {
     if (!r) return fail("gmoe", "out of host memory");
     msynth_router(seed, L, r); msynth_norm(seed, L, nw);
     cudaError_t e1 = cudaMemcpyAsync(l->router, r, (size_t)NEXP * HID * 2, cudaMemcpyHostToDevice, S.st);
-    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s);
+    k_router_pack(S.st, l->router, l->router_t); k_router_pack_small(S.st, l->router, l->router_s); k_router_w16(S.st, l->router, l->router_h, l->wnorm);
     cudaError_t e2 = cudaMemcpyAsync(l->post_ln, nw, HID * 2, cudaMemcpyHostToDevice, S.st);
     cudaError_t e3 = cudaMemcpyAsync(l->tab, S.h_tab, NEXP * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, S.st);
     for (int e = 0; e < NEXP; e++) S.h_dsp[e] = S.h_tab[e].ds;
@@ -378,8 +393,21 @@ static void run_router_relaid(const LayerDev *l, const float *bias, int nb, int 
     else k_router_logits_small(S.st, l->router_s, S.hn, S.hT, relaid, bias, S.logits, nb, S.err);
 }
 static void run_router(const LayerDev *l, const float *bias, int nb) { run_router_relaid(l, bias, nb, 0); }
+/* Which router: 0 = by size (tensor cores from 512 tokens on), 1 = always the exact-order kernels, 2 = tensor cores for every size. */
+int gmoe_set_router(int mode) { if (mode < 0 || mode > 2) return fail("gmoe", "router mode %d", mode); S.router_mode = mode; return 0; }
+static int tensor_router(int nb) { return S.router_mode == 2 || (S.router_mode == 0 && nb >= 512); }
+int gmoe_router_flagged(void) { int n = -1; if (S.ready) { cudaMemcpyAsync(&n, S.nflagged, 4, cudaMemcpyDeviceToHost, S.st); cudaStreamSynchronize(S.st); } return n; }
+/* logits, top-8 and weights on the tensor cores (needs the fp16 terms and norms that k_norm_prep_split left) */
+static void run_router_tensor(const LayerDev *l, const float *bias, int nb) {
+    RouterTensorArgs r; memset(&r, 0, sizeof r);
+    r.amap = S.amap; r.wmap = l->wmap; r.part = S.rpart; r.nb = nb; r.ntok_cap = S.maxtok; r.err = S.err;
+    r.bias = bias; r.hnorm = S.hnorm; r.wnorm = l->wnorm; r.hn = S.hn; r.router_s = l->router_s;
+    r.logits = S.logits; r.top = S.top; r.topw = S.topw; r.flagged = S.flagged; r.nflagged = S.nflagged; r.done = S.rdone;
+    k_router_tensor(S.st, &r);
+}
 /* norm + int8 of the layer's input; decode batches also get the router's layout in the same pass */
 static int run_norm(const float *x, const uint16_t *w, int nb) {
+    if (tensor_router(nb)) { k_norm_prep_split(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, S.hA, S.hnorm, nb); return 0; }
     if (nb < ROUTER_TILE_MIN) { k_norm_prep_relaid(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, (float *)S.hT, nb); return 1; }
     k_norm_prep(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, nb); return 0;
 }
@@ -387,8 +415,11 @@ static int run_norm(const float *x, const uint16_t *w, int nb) {
 static void run_layer(int L, int nb, int norm, const float *bias) {
     LayerDev *l = &S.ly[L];
     prof_begin(0); const int relaid = run_norm(norm ? S.x : S.hn, norm ? l->post_ln : NULL, nb); prof_end(0);
-    prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
-    prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    if (tensor_router(nb)) { prof_begin(1); run_router_tensor(l, bias, nb); prof_end(1); }
+    else {
+        prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
+        prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    }
     prof_begin(3); run_group(nb); prof_end(3);
     run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 7);
     prof_begin(7);
@@ -465,12 +496,12 @@ static int layers_enqueue_ep(int nb, int l0, int nl, const float *bd, int ep) {
     if (!graphs_on()) return layers_run(nb, l0, nl, bd, ep);
     int k = -1, free_k = -1;
     for (int i = 0; i < NGRAPH; i++) {
-        if (GR[i].seen && GR[i].nb == nb && GR[i].l0 == l0 && GR[i].nl == nl && GR[i].bias == (bd != NULL) && GR[i].path == S.path && GR[i].prof == (int)S.prof_mask && GR[i].ep == ep) { k = i; break; }
+        if (GR[i].seen && GR[i].nb == nb && GR[i].l0 == l0 && GR[i].nl == nl && GR[i].bias == (bd != NULL) && GR[i].path == S.path + 8 * S.router_mode && GR[i].prof == (int)S.prof_mask && GR[i].ep == ep) { k = i; break; }
         if (!GR[i].seen && free_k < 0) free_k = i;
     }
     if (k < 0) {   /* first sight: run plainly and remember the key */
         if (layers_run(nb, l0, nl, bd, ep)) return -1;
-        if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path; GR[free_k].prof = (int)S.prof_mask; GR[free_k].ep = ep; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
+        if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path + 8 * S.router_mode; GR[free_k].prof = (int)S.prof_mask; GR[free_k].ep = ep; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
         return 0;
     }
     if (!GR[k].exec) {
@@ -689,6 +720,10 @@ int gmoe_stage(const char *name, int L, int nb) {
     else if (!strcmp(name, "prep")) k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
     else if (!strcmp(name, "router")) run_router(l, NULL, nb);
     else if (!strcmp(name, "router_bias")) run_router(l, S.bias, nb);
+    else if (!strcmp(name, "router_tensor") || !strcmp(name, "router_tensor_bias")) {      /* from hn: fp16 terms, logits, top-8, weights */
+        k_norm_prep_split(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, S.hA, S.hnorm, nb);
+        run_router_tensor(l, name[13] ? S.bias : NULL, nb);
+    }
     else if (!strcmp(name, "topk")) k_topk(S.st, S.logits, S.top, S.topw, nb);
     else if (!strcmp(name, "group")) run_group(nb);
     else if (!strcmp(name, "gateup")) { if (use_umma(nb)) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK); run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 1); }
@@ -950,8 +985,11 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     LayerDev *l = &S.ly[L];
     const int tn = tile_tn(nb), um = use_umma(nb);
     prof_begin(0); const int relaid = run_norm(S.x, l->post_ln, nb); prof_end(0);
-    prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
-    prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    if (tensor_router(nb)) { prof_begin(1); run_router_tensor(l, bias, nb); prof_end(1); }
+    else {
+        prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
+        prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
+    }
     prof_begin(3);
     run_group(nb);
     EpPlanArgs p = {EP.all_cnt, EP.rank, EP.world, EP.dst_base, EP.nu_r, EP.ue_r, EP.ustart_r, EP.total, S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tn, UMMA_TN};

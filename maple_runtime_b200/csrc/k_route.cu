@@ -5,9 +5,11 @@
 // multiply-adds where the reference fuses, IEEE division and round-half-even), so its integer outputs are equal
 // and its fp32 outputs are the same bits as maple.c's CPU path.  File:line citations are into maple.c.
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include "kernels.h"
 #include "dev_math.cuh"
+#include "topk.cuh"
 
 static long g_launches = 0;
 extern "C" void k_count_reset(void) { g_launches = 0; }
@@ -26,11 +28,14 @@ extern "C" void k_count_add(long n) { g_launches += n; }
 // order only below double precision, which the conversion to float absorbs.
 // ------------------------------------------------------------------------------------------------------------
 // hS != NULL: the normalised row is also stored as the decode router wants it, [column / 32][lane j][4 steps] (k_router_tile.cu).
+// hA != NULL: the normalised row is also stored as two fp16 terms, hi = fp16(h) in columns 0..2047 and lo = fp16(h - hi) in columns
+// 2048..4095 of a 4096-column row (the tensor-core router's A operand, k_router_umma.cu), and its Euclidean norm goes to hnorm.
 __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w,
                                                         float *__restrict__ hn, int8_t *__restrict__ q,
-                                                        float *__restrict__ qs, int *__restrict__ qsum, float *__restrict__ hS) {
+                                                        float *__restrict__ qs, int *__restrict__ qsum, float *__restrict__ hS,
+                                                        __half *__restrict__ hA, float *__restrict__ hnorm) {
     __shared__ double sd[8];
-    __shared__ float sf[8];
+    __shared__ float sf[8], sn[8];
     __shared__ int si[8];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)b * HID) + tid * 2;
@@ -64,13 +69,24 @@ __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict_
 #pragma unroll
         for (int j = 0; j < 8; j++) d[j * 4] = v[j];
     }
-    float mx = 0.0f;
+    float mx = 0.0f, n2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+    if (hA) {
+        __align__(16) __half hi[8], lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { hi[i] = __float2half_rn(v[i]); lo[i] = __float2half_rn(v[i] - __half2float(hi[i])); n2 = fmaf(v[i], v[i], n2); }
+        __half *row = hA + (size_t)b * (2 * HID) + tid * 8;
+        *reinterpret_cast<uint4 *>(row) = *reinterpret_cast<const uint4 *>(hi);
+        *reinterpret_cast<uint4 *>(row + HID) = *reinterpret_cast<const uint4 *>(lo);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, o);
+    }
 #pragma unroll
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) sf[wid] = mx;
+    if (lane == 0) { sf[wid] = mx; sn[wid] = n2; }
     __syncthreads();
+    if (hA && tid == 0) hnorm[b] = sqrtf(((sn[0] + sn[1]) + (sn[2] + sn[3])) + ((sn[4] + sn[5]) + (sn[6] + sn[7])));
     mx = fmaxf(fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3])), fmaxf(fmaxf(sf[4], sf[5]), fmaxf(sf[6], sf[7])));
     const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
     int tot = 0; uint32_t pk[2] = {0, 0};
@@ -88,11 +104,15 @@ __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict_
 }
 extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL); g_launches++;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL, NULL, NULL); g_launches++;
 }
 extern "C" void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, hS); g_launches++;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, hS, NULL, NULL); g_launches++;
+}
+extern "C" void k_norm_prep_split(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, void *hA, float *hnorm, int nb) {
+    if (nb <= 0) return;
+    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL, (__half *)hA, hnorm); g_launches++;
 }
 
 // (Router logits live in k_router_tile.cu.)
@@ -106,51 +126,14 @@ __global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ log
     __shared__ unsigned long long tab[32];                  // the expf table beside the arithmetic (lane-varying index)
     if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
     __syncthreads();
-    const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (b >= nb) return;
     const float4 *lr = reinterpret_cast<const float4 *>(logits + (size_t)b * NEXP + lane * 8);
     float4 v0 = lr[0], v1 = lr[1];
     float p[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    float mx = -1e30f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) mx = p[i] > mx ? p[i] : mx;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) { float t = __shfl_xor_sync(0xffffffffu, mx, o); mx = t > mx ? t : mx; }
-#pragma unroll
-    for (int i = 0; i < 8; i++) p[i] = dev_expf_tab(__fsub_rn(p[i], mx), tab);
-    float run = 0.0f;
-    for (int l = 0; l < 32; l++) {
-        if (lane == l) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) run = __fadd_rn(run, p[i]);
-        }
-        run = __shfl_sync(0xffffffffu, run, l);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; i++) p[i] = __fdiv_rn(p[i], run);
-    // Eight rounds of "first strict maximum" (maple.c:917-921).  Probabilities are >= +0, so their bit patterns order like the
-    // values: key = bits + 1, a taken entry becomes 0.  One redux.sync gives the warp's maximum, the lowest lane holding it (and
-    // the lowest of its eight entries) is the first maximum in expert order.
-    unsigned key[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) key[i] = __float_as_uint(p[i]) + 1u;
-    float tsum = 0.0f, wsel = 0.0f; int isel = 0;
-    for (int k = 0; k < TOPK; k++) {
-        unsigned lk = key[0];
-#pragma unroll
-        for (int i = 1; i < 8; i++) lk = max(lk, key[i]);
-        const unsigned m = __reduce_max_sync(0xffffffffu, lk);
-        const int src = __ffs(__ballot_sync(0xffffffffu, lk == m)) - 1;
-        int bi = 7;
-#pragma unroll
-        for (int i = 6; i >= 0; i--) if (key[i] == m) bi = i;
-        const int be = __shfl_sync(0xffffffffu, lane * 8 + bi, src);
-        const float bv = __uint_as_float(m - 1u);
-#pragma unroll
-        for (int i = 0; i < 8; i++) if (lane == src && i == bi) key[i] = 0u;
-        tsum = __fadd_rn(tsum, bv);
-        if (lane == k) { wsel = bv; isel = be; }
-    }
+    int isel; float wsel, tsum;
+    exact_topk_warp(p, lane, tab, isel, wsel, tsum);
     if (lane < TOPK) {
         top[b * TOPK + lane] = isel;
         topw[b * TOPK + lane] = __fdiv_rn(wsel, __fadd_rn(tsum, 1e-20f));

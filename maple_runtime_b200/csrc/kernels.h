@@ -56,6 +56,9 @@ void k_router_pack_small(cudaStream_t st, const uint16_t *router, void *router_s
 void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, int relaid, const float *bias, float *logits, int nb, int *err);
 void k_router_logits_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err);
 void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb);
+/* norm + int8 as k_norm_prep, and the normalised rows once more as two fp16 terms per value (hA: [nb][4096] fp16, hi then lo) with the
+ * rows' Euclidean norms (hnorm [nb]): the A operand of the tensor-core router */
+void k_norm_prep_split(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, void *hA, float *hnorm, int nb);
 typedef struct {
     const int *top; const float *topw; int nb;
     unsigned *mask;          /* [256][mask_words] bit rows, then 256 counters, then [256][mask_words] word prefixes */
@@ -90,6 +93,23 @@ void k_down_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 void k_dense_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
+
+/* ---- router on the tensor cores (k_router_umma.cu): logits, top-8 and weights of nb tokens.  Tokens whose nine largest logits are
+ * too close to call are recomputed in the reference's exact order of operations, so the indices are the reference's for every token;
+ * weights and logits of the other tokens agree with it to ~1e-6. */
+typedef struct {
+    TMap amap;               /* hA [ntok_cap][4096] fp16, box 64 x 128 */
+    TMap wmap;               /* the layer's router rows as fp16 [256][2048], box 64 x 256 (k_router_w16) */
+    float *part;             /* [8][ntok_cap][256] partial sums */
+    int nb, ntok_cap; int *err;
+    const float *bias, *hnorm, *wnorm, *hn;   /* wnorm [1]: largest row norm of the layer's router (k_router_w16) */
+    const void *router_s;    /* the rows re-laid by k_router_pack_small: the exact recomputation reads them */
+    float *logits; int *top; float *topw;
+    int *flagged, *nflagged; /* [nb], [1]: tokens that took the exact path (left for inspection) */
+    int *done;               /* [nb] counters, zero between calls */
+} RouterTensorArgs;
+void k_router_w16(cudaStream_t st, const uint16_t *router, void *w16, float *wnorm);
+void k_router_tensor(cudaStream_t st, const RouterTensorArgs *r);
 
 /* ---- compact down rows (the tcgen05 path) ----
  * The down projection's results leave the expert kernel as integers and are scaled where they are combined: half the bytes of

@@ -24,3 +24,25 @@ out:
     cudaFree(da); cudaFree(db); cudaFree(dd); cudaFree(ds);
     return rc;
 }
+
+int k_i8_peak(cudaStream_t st, int n, int iters, int sms, int *status);
+/* include/gmoe.h: measured tcgen05.mma kind::i8 rate of this GPU, in units of 1e12 integer operations per second */
+double gmoe_i8_peak(int n, int iters) {
+    int dev = 0, sms = 0, hs = 0, *ds = NULL; float ms = 0; double tops = -1.0;
+    cudaEvent_t a = NULL, b = NULL;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) { fprintf(stderr, "gmoe: i8 peak: no CUDA device\n"); return -1.0; }
+    if (cudaMalloc((void **)&ds, 4) != cudaSuccess) { fprintf(stderr, "gmoe: i8 peak: no device memory\n"); return -1.0; }
+    cudaMemset(ds, 0, 4); cudaEventCreate(&a); cudaEventCreate(&b);
+    if (k_i8_peak(0, n, iters, sms, ds)) { fprintf(stderr, "gmoe: i8 peak: n %d, iters %d\n", n, iters); goto out; }   /* warm-up */
+    cudaEventRecord(a, 0);
+    k_i8_peak(0, n, iters, sms, ds);
+    cudaEventRecord(b, 0);
+    if (cudaDeviceSynchronize() != cudaSuccess) { fprintf(stderr, "gmoe: i8 peak: %s\n", cudaGetErrorString(cudaGetLastError())); goto out; }
+    cudaMemcpy(&hs, ds, 4, cudaMemcpyDeviceToHost);
+    if (hs) { fprintf(stderr, "gmoe: i8 peak: an MMA completion never arrived\n"); goto out; }
+    cudaEventElapsedTime(&ms, a, b);
+    tops = 2.0 * 128.0 * n * 32.0 * 4.0 * iters * sms / (ms * 1e-3) / 1e12;
+out:
+    cudaFree(ds); if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b);
+    return tops;
+}

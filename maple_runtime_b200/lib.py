@@ -41,13 +41,13 @@ DECLS = {
     "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),
     "gmoe_set_graph": (i32, [i32]), "gmoe_graph_launches": (C.c_long, []), "gmoe_router_tile_tokens": (None, [i32]), "gmoe_profile": (i32, [C.c_uint]), "gmoe_profile_read": (i32, [vp, vp]), "gmoe_sync": (f64, []), "gmoe_post_norm": (i32, [i32, i32, vp]),
     "gmoe_peek": (i32, [C.c_char_p, vp, sz]), "gmoe_poke": (i32, [C.c_char_p, vp, sz]),
-    "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]),
+    "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]), "gmoe_set_router": (i32, [i32]), "gmoe_router_flagged": (i32, []),
     "gmoe_ep_unique_id": (i32, [vp]), "gmoe_ep_init": (i32, [i32, i32, vp]), "gmoe_ep_handles": (i32, [vp]), "gmoe_ep_connect": (i32, [vp]),
     "gmoe_ep_forward_dev": (i32, [i32, i32, i32, i32, vp]), "gmoe_ep_forward": (f64, [vp, i32, i32, i32, vp]),
     "gmoe_ep_allmax": (i32, [vp]), "gmoe_load_layers": (i32, [C.c_char_p, i32, i32, i32, i32]), "gmoe_load_error": (C.c_char_p, []),
     "gmoe_ep_received": (i32, []), "gmoe_ep_timeout_selftest": (i32, [i32]),
     "gmoe_group_noalloc": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
-    "gmoe_umma_selftest": (i32, [vp, vp, i32, i32, i32, vp]),
+    "gmoe_umma_selftest": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_i8_peak": (f64, [i32, i32]),
     "gmoe_region_read": (i32, [i32, sz, vp, sz]), "gmoe_region_count": (i32, []),
     "gmoe_last_error": (C.c_char_p, []), "gmoe_launch_count": (C.c_long, []),
     "gmoe_pinned_alloc": (vp, [sz]), "gmoe_pinned_free": (None, [vp]), "gmoe_device_info": (i32, [vp, i32, vp, vp]),
@@ -186,6 +186,10 @@ class Gpre:
     def set_path(self, path):
         """0 = by size, 1 = register-decode mma.sync kernels, 2 = tcgen05 kernels."""
         self._chk(self.lib.gmoe_set_path(path))
+
+    def set_router(self, mode):
+        """0 = by size (tensor cores from 512 tokens on), 1 = exact-order kernels always, 2 = tensor cores always."""
+        self._chk(self.lib.gmoe_set_router(mode))
 
     def keep_stages(self, keep=True):
         self._chk(self.lib.gmoe_keep_stages(int(keep)))
