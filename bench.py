@@ -193,8 +193,9 @@ def parity_check(g, ml, nl):
     x = ml.synth_hidden(clib, SEED, 1999, NB)
     use_ref = orc.Reference.available()
     ref = orc.Reference() if use_ref else orc.Oracle()
-    # one thread: the reference's worker threads spin for the life of the process (maple.c:89-108) and would sit on the cores that
-    # the CPU baseline leg times later
+    if use_ref:
+        ref.threads(1)      # one thread: the reference's workers spin for the life of the process (maple.c:89-108) and would sit on
+                            # the cores that the CPU baseline leg times later
     worst, same_top = 0.0, True
     for L in range(nlay):
         lay = (ml.synth_router(clib, SEED, L), ml.synth_norm(clib, SEED, L), ml.synth_experts(clib, SEED, L, 0, 256))

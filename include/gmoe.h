@@ -102,6 +102,11 @@ int gmoe_stage(const char *name, int L, int nb);
  * error bound; 1 = always the exact-order kernels (logits, weights and everything downstream have the reference's bits);
  * 2 = tensor cores for every batch size.  In all modes the top-8 indices are the reference's (maple.c:910-923). */
 int gmoe_set_router(int mode);
+/* The reference computes a lone token's router logits in two different orders: `step` (token-by-token decode, maple.c:609) calls
+ * bf_row (maple.c:146-157: two multiply-add chains per lane), `step_batch` (prefill chunks and --multi, maple.c:734) calls
+ * job_route_small (853-869: one chain per lane).  The bits differ, so a near-tie can choose differently.  on = 1: calls with one
+ * token use the `step` order; on = 0 (default): the `step_batch` order for every size. */
+int gmoe_set_step_order(int on);
 /* tokens of the last tensor-core router call that took the exact path */
 int gmoe_router_flagged(void);
 /* 0 = grouped kernels chosen by size (default), 1 = force the mma.sync register-decode kernels,

@@ -394,6 +394,7 @@ static void run_router_relaid(const LayerDev *l, const float *bias, int nb, int 
 }
 static void run_router(const LayerDev *l, const float *bias, int nb) { run_router_relaid(l, bias, nb, 0); }
 /* Which router: 0 = by size (tensor cores from 512 tokens on), 1 = always the exact-order kernels, 2 = tensor cores for every size. */
+int gmoe_set_step_order(int on) { graphs_drop(); k_router_step_order(on); return 0; }   /* a captured layer loop holds the kernel of the old order */
 int gmoe_set_router(int mode) { if (mode < 0 || mode > 2) return fail("gmoe", "router mode %d", mode); S.router_mode = mode; return 0; }
 static int tensor_router(int nb) { return S.router_mode == 2 || (S.router_mode == 0 && nb >= 512); }
 int gmoe_router_flagged(void) { int n = -1; if (S.ready) { cudaMemcpyAsync(&n, S.nflagged, 4, cudaMemcpyDeviceToHost, S.st); cudaStreamSynchronize(S.st); } return n; }
@@ -472,7 +473,7 @@ static double finish(const char *who) {
  * launchers happen outside a capture).  Per-stage events are captured as event-record nodes, so gmoe_profile_read then reports the
  * last replay.  Not used while stages are kept or when GMOE_GRAPH=0 is set.  Under expert parallelism the ranks make the same calls
  * in the same order, so they capture and replay together; nothing on that path calls NCCL. */
-#define NGRAPH 16
+#define NGRAPH 64
 static struct { int nb, l0, nl, bias, path, prof, ep, seen; long launches; cudaGraphExec_t exec; } GR[NGRAPH];
 static int g_graph_on = -1;
 static long g_graph_launches;
@@ -501,6 +502,13 @@ static int layers_enqueue_ep(int nb, int l0, int nl, const float *bd, int ep) {
     }
     if (k < 0) {   /* first sight: run plainly and remember the key */
         if (layers_run(nb, l0, nl, bd, ep)) return -1;
+        if (free_k < 0) {   /* table full: the slots are reused in turn */
+            static int victim;
+            free_k = victim; victim = (victim + 1) % NGRAPH;
+            cudaStreamSynchronize(S.st);
+            if (GR[free_k].exec) cudaGraphExecDestroy(GR[free_k].exec);
+            memset(&GR[free_k], 0, sizeof GR[free_k]);
+        }
         if (free_k >= 0) { GR[free_k].nb = nb; GR[free_k].l0 = l0; GR[free_k].nl = nl; GR[free_k].bias = bd != NULL; GR[free_k].path = S.path + 8 * S.router_mode; GR[free_k].prof = (int)S.prof_mask; GR[free_k].ep = ep; GR[free_k].seen = 1; GR[free_k].exec = NULL; }
         return 0;
     }

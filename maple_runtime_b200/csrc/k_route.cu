@@ -146,27 +146,29 @@ extern "C" void k_topk(cudaStream_t st, const float *logits, int *top, float *to
 
 // ------------------------------------------------------------------------------------------------------------
 // Grouping (maple.c:924-938) and tp (maple.c:1018-1019), deterministic without ordered atomics:
-//   1. mark:  bit b of mask[e] is set when token b chose expert e (atomicOr: the result does not depend on order)
-//   2. scan:  used experts are numbered in ascending order (NU, UE, USTART), the tile lists for the grouped GEMMs are
-//             written, and for every expert and 32-token word the slot of the word's first token
-//   3. place: one thread per token: pair slot = word prefix + rank inside the word; UTOK, UW, the slot of every
-//             (token, choice), and tp = the token's eight slots sorted ascending (pair index order = expert order)
+//   1. mark:  bit (b % 32) of mask[b / 32][e] is set when token b chose expert e (atomicOr: the result does not depend on order),
+//             and the pairs of every expert are counted (integer adds: any order, same sum)
+//   2. place: a CTA owns 128 tokens (four mask words).  Thread e scans the counts into the experts' starts (used experts numbered in
+//             ascending order: NU, UE, USTART; CTA 0 writes them and the tile lists of the grouped GEMMs) and counts expert e's
+//             tokens in front of the CTA's words; then one thread per token: pair slot = start + tokens in front + rank inside the
+//             word; UTOK, UW, the slot of every (token, choice), and tp = the token's eight slots sorted ascending (pair index
+//             order = expert order)
 // ------------------------------------------------------------------------------------------------------------
 __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restrict__ mask, int mask_words, int np) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= np) return;
     int b = i >> 3, e = top[i];
-    atomicOr(&mask[(size_t)e * mask_words + (b >> 5)], 1u << (b & 31));
-    atomicAdd(&mask[(size_t)NEXP * mask_words + e], 1u);        // pairs per expert, kept behind the bit rows (integer adds: any order, same sum)
+    atomicOr(&mask[(size_t)(b >> 5) * NEXP + e], 1u << (b & 31));
+    atomicAdd(&mask[(size_t)NEXP * mask_words + e], 1u);        // pairs per expert, kept behind the bit words
 }
-// scan + word prefixes: 32 CTAs of 256 threads.  Every CTA repeats the scan over the 256 experts (cheap) so that its eight warps
-// know where their experts start; CTA 0 alone writes the compact lists and the tiles.  Warp w of CTA c then takes expert 8c + w and
-// writes, for every 32-token word of its bit row, how many of its tokens come before that word.
-__global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__restrict__ mask, int mask_words, int *__restrict__ nu_out,
-                                                          int *__restrict__ ue, int *__restrict__ estart, int *__restrict__ ustart, int *__restrict__ ecnt,
-                                                          MoeTile *__restrict__ ta, int *__restrict__ nta, int tna,
-                                                          MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb, int *__restrict__ wprefix) {
-    __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8], s_start[NEXP];
+__global__ void __launch_bounds__(NEXP) group_place_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ top,
+                                                          const float *__restrict__ topw, int *__restrict__ nu_out, int *__restrict__ ue,
+                                                          int *__restrict__ estart, int *__restrict__ ustart, int *__restrict__ ecnt,
+                                                          MoeTile *__restrict__ ta, int *__restrict__ nta, int tna, MoeTile *__restrict__ tb, int *__restrict__ ntb, int tnb,
+                                                          int *__restrict__ utok, float *__restrict__ uw, int *__restrict__ slot, int *__restrict__ uexp,
+                                                          int *__restrict__ tp, int nb) {
+    __shared__ int w_cnt[8], w_used[8], w_ta[8], w_tb[8];
+    __shared__ int s_pre[4][NEXP]; __shared__ unsigned s_word[4][NEXP];
     const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
     const int cnt = (int)mask[(size_t)NEXP * mask_words + e];
     const int used = cnt > 0, na = (cnt + tna - 1) / tna, nb_ = (cnt + tnb - 1) / tnb;
@@ -182,7 +184,6 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
     int oc = 0, ou = 0, oa = 0, ob = 0;
     for (int w = 0; w < wid; w++) { oc += w_cnt[w]; ou += w_used[w]; oa += w_ta[w]; ob += w_tb[w]; }
     const int start = oc + c - cnt, uidx = ou + u - used, ta0 = oa + a - na, tb0 = ob + b - nb_;
-    s_start[e] = start;
     if (blockIdx.x == 0) {
         if (ecnt) ecnt[e] = cnt;
         estart[e] = used ? start : -1;
@@ -193,39 +194,33 @@ __global__ void __launch_bounds__(NEXP) group_scan_kernel(const unsigned *__rest
         }
         if (e == NEXP - 1) { const int nu = uidx + used; *nu_out = nu; ustart[nu] = start + cnt; *nta = ta0 + na; *ntb = tb0 + nb_; }
     }
-    __syncthreads();
-    const int ex = blockIdx.x * 8 + wid;                     // this warp's expert
-    int run = s_start[ex];
-    for (int w0 = 0; w0 < mask_words; w0 += 32) {
-        const int w = w0 + lane;
-        const int pc = w < mask_words ? __popc(mask[(size_t)ex * mask_words + w]) : 0;
-        int incl = pc;
+    // expert e's tokens in front of this CTA's four words (coalesced: consecutive threads read consecutive experts of a word)
+    const int w0 = blockIdx.x * 4;
+    int pre = start;
+    for (int w = 0; w < w0; w++) pre += __popc(mask[(size_t)w * NEXP + e]);
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-        if (w < mask_words) wprefix[(size_t)ex * mask_words + w] = run + incl - pc;       // slot of the word's first token
-        run += __shfl_sync(0xffffffffu, incl, 31);
+    for (int k = 0; k < 4; k++) {
+        const unsigned word = w0 + k < mask_words ? mask[(size_t)(w0 + k) * NEXP + e] : 0u;
+        s_pre[k][e] = pre; s_word[k][e] = word; pre += __popc(word);
     }
-}
-// one thread per token: the slot of each of its eight pairs = the word prefix + the rank inside the word; the pair lists and tp
-__global__ void __launch_bounds__(128) group_place_kernel(const unsigned *__restrict__ mask, int mask_words, const int *__restrict__ wprefix,
-                                                          const int *__restrict__ top, const float *__restrict__ topw, int *__restrict__ utok,
-                                                          float *__restrict__ uw, int *__restrict__ slot, int *__restrict__ uexp, int *__restrict__ tp, int nb) {
-    const int b = blockIdx.x * 128 + threadIdx.x;
-    if (b >= nb) return;
-    const int w = b >> 5; const unsigned below = (1u << (b & 31)) - 1u;
+    __syncthreads();
+    if (e >= 128) return;
+    const int tok = blockIdx.x * 128 + e;
+    if (tok >= nb) return;
+    const int wk = e >> 5; const unsigned below = (1u << (e & 31)) - 1u;
     int sl[TOPK];
 #pragma unroll
     for (int k = 0; k < TOPK; k++) {
-        const int e = top[b * TOPK + k];
-        const int r = wprefix[(size_t)e * mask_words + w] + __popc(mask[(size_t)e * mask_words + w] & below);
-        sl[k] = r; slot[b * TOPK + k] = r; utok[r] = b; uw[r] = topw[b * TOPK + k]; if (uexp) uexp[r] = e;
+        const int x = top[tok * TOPK + k];
+        const int r = s_pre[wk][x] + __popc(s_word[wk][x] & below);
+        sl[k] = r; slot[tok * TOPK + k] = r; utok[r] = tok; uw[r] = topw[tok * TOPK + k]; if (uexp) uexp[r] = x;
     }
 #pragma unroll
     for (int i = 1; i < TOPK; i++)
 #pragma unroll
         for (int k = TOPK - 1; k >= 1; k--) if (k >= i && sl[k] < sl[k - 1]) { int x = sl[k]; sl[k] = sl[k - 1]; sl[k - 1] = x; }
 #pragma unroll
-    for (int k = 0; k < TOPK; k++) tp[b * TOPK + k] = sl[k];
+    for (int k = 0; k < TOPK; k++) tp[tok * TOPK + k] = sl[k];
 }
 // Decode batches (up to 256 tokens = 2048 pairs): the whole grouping in one CTA, so that the step costs one launch instead of five, and without a
 // serial walk: every pair sets its token's bit in its expert's row of a shared-memory bit table; an expert's
@@ -307,13 +302,12 @@ extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
     if (g->nb <= 256) { launch_group_cta<256, 256>(st, g); g_launches++; return; }
     const int np = g->nb * TOPK;
-    cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit rows + the 256 counters behind them
+    cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit words + the 256 counters behind them
     group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
-    int *wprefix = reinterpret_cast<int *>(g->mask + (size_t)NEXP * g->mask_words + NEXP);    // behind the bit rows and the counters
-    group_scan_kernel<<<NEXP / 8, NEXP, 0, st>>>(g->mask, g->mask_words, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
-                                                 g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b, wprefix);
-    group_place_kernel<<<(g->nb + 127) / 128, 128, 0, st>>>(g->mask, g->mask_words, wprefix, g->top, g->topw, g->utok, g->uw, g->slot, g->uexp, g->tp, g->nb);
-    g_launches += 3;
+    group_place_kernel<<<(g->nb + 127) / 128, NEXP, 0, st>>>(g->mask, g->mask_words, g->top, g->topw, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
+                                                            g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b,
+                                                            g->utok, g->uw, g->slot, g->uexp, g->tp, g->nb);
+    g_launches += 2;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -350,7 +344,24 @@ extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs
 // ------------------------------------------------------------------------------------------------------------
 // SiLU*up + int8 in one pass (maple.c:825-832) for the tensor-core path, whose GEMM stores gate and up: one warp per
 // pair, 16 values per lane.  act (optional) receives the fp32 activations for stage comparisons.
+//
+// The int8 row, its scale and its sum are the reference's bits in both variants.  EXACT evaluates every element with the libm-equal
+// expf in double (dev_math.cuh).  The other variant evaluates act ~ g / (1 + 2^(-g log2 e)) u with the hardware's approximate
+// exponential and reciprocal (relative error below SQ_EPS for every g <= 7 that does not underflow) and falls back to the exact
+// evaluation only where the approximation could change a result:
+//   * the row maximum: every element within 2 SQ_EPS of the approximate maximum is evaluated exactly, the exact maximum is among them;
+//   * a rounded value: t = act * inv lands within |t| (2 SQ_EPS + 2^-22) of a rounding boundary (about one element in two thousand).
 // ------------------------------------------------------------------------------------------------------------
+#define SQ_EPS 1.2e-5f
+__device__ __forceinline__ float silu_mul_approx(float g, float u) {
+    g = g < 7.0f ? g : 7.0f;
+    u = u < -7.0f ? -7.0f : (u > 7.0f ? 7.0f : u);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r * u;
+}
+template <bool EXACT>
 __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
                                                          int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np, const int *__restrict__ np_dev) {
     if (np_dev) np = min(np, *np_dev);
@@ -361,27 +372,52 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
     if (a >= np) return;
     const float4 *gr = reinterpret_cast<const float4 *>(gate + (size_t)a * FFN) + lane * 4;
     const float4 *ur = reinterpret_cast<const float4 *>(up + (size_t)a * FFN) + lane * 4;
-    float v[16];
+    float gv[16], uv[16], v[16];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const float4 g = gr[i], u = ur[i];
-        v[4 * i] = dev_silu_mul_tab(g.x, u.x, tab); v[4 * i + 1] = dev_silu_mul_tab(g.y, u.y, tab);
-        v[4 * i + 2] = dev_silu_mul_tab(g.z, u.z, tab); v[4 * i + 3] = dev_silu_mul_tab(g.w, u.w, tab);
-    }
-    if (act) {
-        float4 *o = reinterpret_cast<float4 *>(act + (size_t)a * FFN) + lane * 4;
-#pragma unroll
-        for (int i = 0; i < 4; i++) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        gv[4 * i] = g.x; gv[4 * i + 1] = g.y; gv[4 * i + 2] = g.z; gv[4 * i + 3] = g.w;
+        uv[4 * i] = u.x; uv[4 * i + 1] = u.y; uv[4 * i + 2] = u.z; uv[4 * i + 3] = u.w;
     }
     float mx = 0.0f;
+    if (EXACT) {
 #pragma unroll
-    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(v[i]));
+        for (int i = 0; i < 16; i++) { v[i] = dev_silu_mul_tab(gv[i], uv[i], tab); mx = fmaxf(mx, fabsf(v[i])); }
+        if (act) {
+            float4 *o = reinterpret_cast<float4 *>(act + (size_t)a * FFN) + lane * 4;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            for (int i = 0; i < 4; i++) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    } else {
+        float mxa = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i++) { v[i] = silu_mul_approx(gv[i], uv[i]); mxa = fmaxf(mxa, fabsf(v[i])); }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, o));
+        const float thr = mxa * (1.0f - 2.5f * SQ_EPS) - 1e-30f;      // every element that can be the exact maximum
+#pragma unroll
+        for (int i = 0; i < 16; i++) if (!(fabsf(v[i]) < thr)) mx = fmaxf(mx, fabsf(dev_silu_mul_tab(gv[i], uv[i], tab)));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
     const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
     int tot = 0; uint32_t pk[4] = {0, 0, 0, 0};
+    if (EXACT) {
 #pragma unroll
-    for (int i = 0; i < 16; i++) { int qi = __float2int_rn(__fmul_rn(v[i], inv)); tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3)); }
+        for (int i = 0; i < 16; i++) { int qi = __float2int_rn(__fmul_rn(v[i], inv)); tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3)); }
+    } else {
+        const float slack = 1e-36f * inv;                                // elements the approximation flushed to zero
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const float t = __fmul_rn(v[i], inv), big = __fadd_rn(t, 12582912.0f), r = __fsub_rn(big, 12582912.0f);      // r = t rounded to an integer, half to even
+            int qi = __float_as_int(big) - 0x4B400000;
+            if (!(0.5f - fabsf(__fsub_rn(t, r)) > fabsf(t) * (2.0f * SQ_EPS + 2.4e-7f) + slack))
+                qi = __float2int_rn(__fmul_rn(dev_silu_mul_tab(gv[i], uv[i], tab), inv));
+            tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3));
+        }
+    }
     reinterpret_cast<uint4 *>(aq + (size_t)a * FFN)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
 #pragma unroll
     for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
@@ -389,7 +425,9 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
 }
 extern "C" void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np, const int *np_dev) {
     if (np <= 0) return;
-    silu_quant_kernel<<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np, np_dev); g_launches++;
+    if (act) silu_quant_kernel<true><<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np, np_dev);
+    else silu_quant_kernel<false><<<(np + 7) / 8, 256, 0, st>>>(gate, up, NULL, aq, aqs, aqsum, np, np_dev);
+    g_launches++;
 }
 
 // ------------------------------------------------------------------------------------------------------------

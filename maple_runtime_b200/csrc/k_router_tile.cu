@@ -221,6 +221,9 @@ __global__ void __launch_bounds__(256) router_pack_h_small_kernel(const float *_
     const float *r = hn + (size_t)b * HID + 32 * i4 + j;
     hS[o] = make_float4(r[0], r[8], r[16], r[24]);
 }
+// STEP: the order of the reference's single-token decode (bf_row, maple.c:146-157, called at maple.c:609): per lane two chains, one over
+// columns 16m + j and one over 16m + 8 + j, added before the lanes are; otherwise one chain per lane (job_route_small/multi).
+template <bool STEP>
 __global__ void __launch_bounds__(256, 2) router_small_kernel(const uint8_t *__restrict__ WS, const uint8_t *__restrict__ hS, const float *__restrict__ bias,
                                                              float *__restrict__ logits, int nb, int *err) {
     extern __shared__ __align__(128) uint8_t rs_sm[];                  // hidden 64 KB, then weights 32 KB
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(256, 2) router_small_kernel(const uint8_t *__r
         bulk_load(smem_u32(rs_sm + RS_HB), WS + (size_t)e0 * HID * 2, RS_WB, &bar);
     }
     const bool ok = mbar_wait(&bar, 0, &abort_flag);
-    float acc0 = 0.0f, acc1 = 0.0f;
+    float acc0 = 0.0f, acc1 = 0.0f, odd0 = 0.0f, odd1 = 0.0f;       // odd0/odd1: the second chain of the step order (columns 16m + 8 + j)
     if (ok && tok < ntok) {
         const uint8_t *hp = rs_sm + tok * (HID * 4) + j * 16;
         const uint8_t *w0p = rs_sm + RS_HB + (2 * ep) * (HID * 2) + j * 8, *w1p = w0p + HID * 2;
@@ -244,10 +247,13 @@ __global__ void __launch_bounds__(256, 2) router_small_kernel(const uint8_t *__r
             const float4 h = *reinterpret_cast<const float4 *>(hp + i4 * 128);
             const uint2 a = *reinterpret_cast<const uint2 *>(w0p + i4 * 64), b = *reinterpret_cast<const uint2 *>(w1p + i4 * 64);
             acc0 = __fmaf_rn(__uint_as_float(a.x << 16), h.x, acc0); acc1 = __fmaf_rn(__uint_as_float(b.x << 16), h.x, acc1);
-            acc0 = __fmaf_rn(__uint_as_float(a.x & 0xFFFF0000u), h.y, acc0); acc1 = __fmaf_rn(__uint_as_float(b.x & 0xFFFF0000u), h.y, acc1);
+            if (STEP) { odd0 = __fmaf_rn(__uint_as_float(a.x & 0xFFFF0000u), h.y, odd0); odd1 = __fmaf_rn(__uint_as_float(b.x & 0xFFFF0000u), h.y, odd1); }
+            else { acc0 = __fmaf_rn(__uint_as_float(a.x & 0xFFFF0000u), h.y, acc0); acc1 = __fmaf_rn(__uint_as_float(b.x & 0xFFFF0000u), h.y, acc1); }
             acc0 = __fmaf_rn(__uint_as_float(a.y << 16), h.z, acc0); acc1 = __fmaf_rn(__uint_as_float(b.y << 16), h.z, acc1);
-            acc0 = __fmaf_rn(__uint_as_float(a.y & 0xFFFF0000u), h.w, acc0); acc1 = __fmaf_rn(__uint_as_float(b.y & 0xFFFF0000u), h.w, acc1);
+            if (STEP) { odd0 = __fmaf_rn(__uint_as_float(a.y & 0xFFFF0000u), h.w, odd0); odd1 = __fmaf_rn(__uint_as_float(b.y & 0xFFFF0000u), h.w, odd1); }
+            else { acc0 = __fmaf_rn(__uint_as_float(a.y & 0xFFFF0000u), h.w, acc0); acc1 = __fmaf_rn(__uint_as_float(b.y & 0xFFFF0000u), h.w, acc1); }
         }
+        if (STEP) { acc0 = __fadd_rn(acc0, odd0); acc1 = __fadd_rn(acc1, odd1); }
     }
     // the eight lanes of a position sit in one warp: (l0+l4)+(l1+l5) then +(l2+l6)+(l3+l7), the same on every lane
     float l0 = acc0, l1 = acc1;
@@ -265,11 +271,19 @@ extern "C" void k_router_pack_small(cudaStream_t st, const uint16_t *router, voi
     router_pack_w_small_kernel<<<NEXP * HID / 4 / 256, 256, 0, st>>>(router, (uint2 *)router_s);
     k_count_add(1);
 }
+static int g_step_order = 0;
+// single-token calls compute their logits in the order of the reference's `step` (bf_row) instead of `step_batch` (gmoe_set_step_order)
+extern "C" void k_router_step_order(int on) { g_step_order = on != 0; }
 extern "C" void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, int relaid, const float *bias, float *logits, int nb, int *err) {
     if (nb <= 0) return;
     static bool attr_done = false;
-    if (!attr_done) { cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB); attr_done = true; }
+    if (!attr_done) {
+        cudaFuncSetAttribute(router_small_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB);
+        cudaFuncSetAttribute(router_small_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB); attr_done = true;
+    }
     if (!relaid) router_pack_h_small_kernel<<<nb * 2, 256, 0, st>>>(hn, (float4 *)hS, nb);
-    router_small_kernel<<<dim3(NEXP / RS_EXP, (nb + RS_TOK - 1) / RS_TOK), 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
+    const dim3 grid(NEXP / RS_EXP, (nb + RS_TOK - 1) / RS_TOK);
+    if (g_step_order && nb == 1) router_small_kernel<true><<<grid, 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
+    else router_small_kernel<false><<<grid, 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
     k_count_add(relaid ? 1 : 2);
 }

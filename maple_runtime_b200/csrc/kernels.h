@@ -53,6 +53,7 @@ void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, floa
 void k_router_pack(cudaStream_t st, const uint16_t *router, void *router_t);
 /* decode batches: router_s = the rows re-laid by k_router_pack_small (NEXP*HID*2 bytes), hS = scratch of nb*HID*4 bytes */
 void k_router_pack_small(cudaStream_t st, const uint16_t *router, void *router_s);
+void k_router_step_order(int on);   /* nb == 1: the order of maple.c's bf_row (two chains per lane) instead of job_route_small's */
 void k_router_logits_small(cudaStream_t st, const void *router_s, const float *hn, void *hS, int relaid, const float *bias, float *logits, int nb, int *err);
 void k_router_logits_tile(cudaStream_t st, const void *router_t, const float *hn, void *hT, const float *bias, float *logits, int nb, int *err);
 void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb);
@@ -61,7 +62,7 @@ void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb)
 void k_norm_prep_split(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, void *hA, float *hnorm, int nb);
 typedef struct {
     const int *top; const float *topw; int nb;
-    unsigned *mask;          /* [256][mask_words] bit rows, then 256 counters, then [256][mask_words] word prefixes */
+    unsigned *mask;          /* [mask_words][256] bit words (bit b % 32 of word b / 32: token b chose the expert), then 256 counters */
     int mask_words;
     int *nu, *ue, *estart, *ustart, *utok, *slot, *tp; float *uw;
     int *ecnt, *uexp;        /* optional: pairs per expert [256], expert of every pair [np] (expert parallel) */

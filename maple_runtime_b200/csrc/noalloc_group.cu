@@ -22,7 +22,7 @@
 #define NA_TILES (NA_MAXTOK * 8 / 8 + 256)
 
 struct NaScratch {
-    unsigned mask[2 * 256 * NA_WORDS + 256]; // bit b of row e: token b chose expert e, one counter per expert (both zero at the start of a call), word prefixes
+    unsigned mask[256 * NA_WORDS + 256]; // bit b % 32 of word [b / 32][e]: token b chose expert e; then one counter per expert (all zero at the start of a call)
     int estart[256];
     int slot[NA_MAXTOK * 8];
     MoeTile tiles_a[NA_TILES], tiles_b[NA_TILES];
@@ -66,7 +66,7 @@ extern "C" int gmoe_group_noalloc(const int *top, const float *topw, int nb, int
     g.nu = nu; g.ue = ue; g.estart = s->estart; g.ustart = ustart; g.utok = utok; g.slot = s->slot; g.tp = tp; g.uw = uw;
     g.ecnt = NULL; g.uexp = NULL;
     g.tiles_a = s->tiles_a; g.tiles_b = s->tiles_b; g.ntiles_a = s->ntiles_a; g.ntiles_b = s->ntiles_b; g.tn_a = 8; g.tn_b = UMMA_TN;
-    k_group(static_cast<cudaStream_t>(stream), &g);   // above 256 tokens: clears the masks and counters (cudaMemsetAsync), then three kernels; up to 256: one kernel with its masks in shared memory; no allocation either way
+    k_group(static_cast<cudaStream_t>(stream), &g);   // above 256 tokens: clears the masks and counters (cudaMemsetAsync), then two kernels; up to 256: one kernel with its masks in shared memory; no allocation either way
     e = cudaGetLastError();
     if (e != cudaSuccess) { fprintf(stderr, "gmoe: gmoe_group_noalloc: launch failed: %s\n", cudaGetErrorString(e)); return -3; }
     return 0;

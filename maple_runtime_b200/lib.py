@@ -41,7 +41,7 @@ DECLS = {
     "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),
     "gmoe_set_graph": (i32, [i32]), "gmoe_graph_launches": (C.c_long, []), "gmoe_router_tile_tokens": (None, [i32]), "gmoe_profile": (i32, [C.c_uint]), "gmoe_profile_read": (i32, [vp, vp]), "gmoe_sync": (f64, []), "gmoe_post_norm": (i32, [i32, i32, vp]),
     "gmoe_peek": (i32, [C.c_char_p, vp, sz]), "gmoe_poke": (i32, [C.c_char_p, vp, sz]),
-    "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]), "gmoe_set_router": (i32, [i32]), "gmoe_router_flagged": (i32, []),
+    "gmoe_keep_stages": (i32, [i32]), "gmoe_stage": (i32, [C.c_char_p, i32, i32]), "gmoe_set_path": (i32, [i32]), "gmoe_set_router": (i32, [i32]), "gmoe_router_flagged": (i32, []), "gmoe_set_step_order": (i32, [i32]),
     "gmoe_ep_unique_id": (i32, [vp]), "gmoe_ep_init": (i32, [i32, i32, vp]), "gmoe_ep_handles": (i32, [vp]), "gmoe_ep_connect": (i32, [vp]),
     "gmoe_ep_forward_dev": (i32, [i32, i32, i32, i32, vp]), "gmoe_ep_forward": (f64, [vp, i32, i32, i32, vp]),
     "gmoe_ep_allmax": (i32, [vp]), "gmoe_load_layers": (i32, [C.c_char_p, i32, i32, i32, i32]), "gmoe_load_error": (C.c_char_p, []),

@@ -80,6 +80,11 @@ class Oracle:
         nb = hn.shape[0]; out = np.zeros((nb, NE), np.float32)
         self.lib.orc_router_logits(_p(router), _p(hn), nb, _p(out)); return out
 
+    def router_logits_step(self, router, hn_row):
+        """bf_row order (maple.c:146-157), one token."""
+        out = np.zeros(NE, np.float32)
+        self.lib.orc_router_logits_step(_p(router), _p(np.ascontiguousarray(hn_row, np.float32)), _p(out)); return out
+
     def topk(self, logits_row):
         lg = np.array(logits_row, np.float32, copy=True); top = np.zeros(TOPK, np.int32); w = np.zeros(TOPK, np.float32)
         self.lib.orc_topk(_p(lg), _p(top), _p(w)); return top, w, lg
@@ -107,6 +112,7 @@ class Reference:
         L.rh_expf.restype = C.c_float; L.rh_expf.argtypes = [C.c_float]
         L.rh_tdot.restype = C.c_float; L.rh_tdot.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp]
         self._keep = {}
+        L.rh_threads(1)   # maple.c starts with NT = 4 and no workers running: without this its run() would wait for threads that do not exist
 
     @staticmethod
     def available(fast=False):

@@ -356,3 +356,66 @@ def test_loader_reads_a_converted_directory(layers, clib, weights, tmp_path):
     assert same_bits(y, want)
     assert g.lib.gmoe_load_layers(str(tmp_path).encode(), 1, 1, 8, 0) == -1 and b"no layer 1" in g.lib.gmoe_load_error()
     assert g.lib.gmoe_load_layers(str(tmp_path / "nowhere").encode(), 0, 1, 8, 0) == -1
+
+
+def test_single_token_step_order_router(layers, clib, oracle, weights):
+    """One token in the order of the reference's `step` (bf_row, maple.c:146-157, 609): logits bit for bit against the oracle's
+    statement of that order, which differs from the step_batch order in the last bits; top-8 and weights follow from those logits."""
+    g = layers
+    router, _, _ = weights.layer(2)
+    differ = 0
+    try:
+        for stream in range(700, 708):
+            hn = weights.hidden(stream, 1)
+            want_step, want_batch = oracle.router_logits_step(router, hn[0]), oracle.router_logits(router, hn)[0]
+            differ += int((want_step.view(np.uint32) != want_batch.view(np.uint32)).sum())
+            g.poke("hn", hn)
+            clib.gmoe_set_step_order(1)
+            g.stage("router", 2, 1)
+            assert same_bits(g.peek("logits", 1).reshape(256), want_step)
+            g.stage("topk", 2, 1)
+            top, w, _ = oracle.topk(want_step)
+            assert np.array_equal(g.peek("top", 1).reshape(8), top) and same_bits(g.peek("topw", 1).reshape(8), w)
+            clib.gmoe_set_step_order(0)
+            g.stage("router", 2, 1)
+            assert same_bits(g.peek("logits", 1).reshape(256), want_batch)
+    finally:
+        clib.gmoe_set_step_order(0)
+    assert differ > 0          # the two orders are not the same arithmetic
+
+
+def test_fast_silu_int8_equals_exact_variant(layers, oracle):
+    """The SiLU*up + int8 kernel the timed path runs (hardware exp/reciprocal, exact re-evaluation near the row maximum and near rounding
+    boundaries) against the variant that evaluates every element with the libm-equal expf: int8 rows, scales and sums must be the same
+    bits, on ordinary values and on rows built to stress the fall-backs; a sample of rows also against the oracle's prep (maple.c:184-194,
+    825-832)."""
+    g = layers
+    nb = 2048; P = nb * 8
+    rng = np.random.default_rng(77)
+    gate = (rng.standard_normal((P, 512)) * 3.0).astype(np.float32)
+    up = (rng.standard_normal((P, 512)) * 2.0).astype(np.float32)
+    gate[100:200] *= 10.0                                    # clamped at 7 above, deep negative tails below
+    gate[200:260] = -np.abs(gate[200:260]) * 25.0            # exp(-g) up to overflow: act = -0 or denormal
+    up[260:300] = 0.0                                        # all-zero rows: scale 1
+    gate[300:340] *= 1e-20; up[300:340] *= 1e-18             # tiny rows: the absolute slack takes over
+    gate[340:400, :] = gate[340:400, :1]; up[340:400, :] = up[340:400, :1]   # 512 equal values: every element is a maximum candidate
+    up[400:500] = np.where(rng.random((100, 512)) < 0.5, 7.5, -7.5)          # clamped |u| = 7, many near-equal maxima
+    gate[500:600] = np.float32(7.0) + rng.integers(-3, 4, (100, 512)).astype(np.float32) * np.float32(2.0 ** -20)   # around the clamp
+    g.set_path(2)
+    try:
+        g.poke("gate", gate); g.poke("up", up)
+        g.keep_stages(True)
+        g.stage("actq", 0, nb)
+        want = {k: g.peek(k, nb).copy() for k in ("aq", "aqs", "aqsum", "act")}
+        g.poke("aq", np.zeros((P, 512), np.int8))
+        g.keep_stages(False)
+        g.stage("actq", 0, nb)
+        got = {k: g.peek(k, nb) for k in ("aq", "aqs", "aqsum")}
+    finally:
+        g.keep_stages(True); g.set_path(0)
+    bad = np.argwhere(got["aq"] != want["aq"])
+    assert bad.size == 0, f"{len(bad)} int8 values differ, first at {bad[:3].tolist()}"
+    assert same_bits(got["aqs"], want["aqs"]) and np.array_equal(got["aqsum"], want["aqsum"])
+    for a in list(range(601, P, 997)) + [150, 270, 350, 450, 550]:     # the exact variant itself against the oracle's prep of its act row (rows of ordinary magnitude)
+        q, qs, qsum = oracle.prep(want["act"][a])
+        assert np.array_equal(q, want["aq"][a]) and np.float32(qs).tobytes() == want["aqs"][a].tobytes() and qsum == want["aqsum"][a]
