@@ -160,7 +160,11 @@ __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_consta
 __global__ void __launch_bounds__(256) router_select_kernel(const float *__restrict__ part, int ntok_cap, const float *__restrict__ bias,
                                                             const float *__restrict__ hnorm, const float *__restrict__ wnorm,
                                                             float *__restrict__ logits, int *__restrict__ top, float *__restrict__ topw,
-                                                            int *__restrict__ flagged, int *__restrict__ nflagged, int nb) {
+                                                            int *__restrict__ flagged, int *__restrict__ nflagged, const uint8_t *__restrict__ router_s, int nb) {
+    {   // the flagged tokens' recomputation reads the layer's re-laid router rows (1 MB) right after this kernel: pull them into L2 now
+        const unsigned line = blockIdx.x * 256u + threadIdx.x;
+        if (line < NEXP * HID * 2 / 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(router_s + (size_t)line * 128));
+    }
     const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (b >= nb) return;
     float l[8];
@@ -286,7 +290,7 @@ extern "C" void k_router_tensor(cudaStream_t st, const RouterTensorArgs *r) {
     if (!attr_done) { cudaFuncSetAttribute(router_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_done = true; }
     cudaMemsetAsync(r->nflagged, 0, 4, st);
     router_umma_kernel<<<dim3(RU_KS, (r->nb + 127) / 128), 192, smem, st>>>(r->amap, r->wmap, r->part, r->nb, r->ntok_cap, r->err);
-    router_select_kernel<<<(r->nb + 7) / 8, 256, 0, st>>>(r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->nb);
+    router_select_kernel<<<(r->nb + 7) / 8, 256, 0, st>>>(r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, (const uint8_t *)r->router_s, r->nb);
     router_fix_kernel<<<dim3(8, 74), 256, 0, st>>>((const uint8_t *)r->router_s, r->hn, r->bias, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->done, r->nb);
     k_count_add(3);
 }

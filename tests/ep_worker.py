@@ -61,6 +61,7 @@ def main():
         for L in range(layers):
             g.synth_layer(SEED, L, rank * epr, epr)             # only this rank's experts live on this GPU
         ep.setup(g, rank, world, gather)
+        g.set_router(1)                                         # exact-order router: the comparison below is bit for bit through all layers
         bias = ml.synth_zipf_bias(clib, SEED) if zipf else None
         x = ml.synth_hidden(clib, SEED, 500 + rank, nb)
         want = x.copy()
