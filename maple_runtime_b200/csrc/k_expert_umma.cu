@@ -142,7 +142,11 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             MoeTile tnext = blockIdx.x < nitems ? a.tiles[blockIdx.x / MB] : MoeTile{0, 0, 0, 0};      // one item ahead: no load latency at an item's start
             for (int item = blockIdx.x; item < nitems && live; item += gridDim.x) {
                 const MoeTile tile = tnext;
-                if (item + (int)gridDim.x < nitems) tnext = a.tiles[(item + gridDim.x) / MB];
+                if (item + (int)gridDim.x < nitems) {
+                    tnext = a.tiles[(item + gridDim.x) / MB];
+                    const ExpertMaps *en = a.maps + tnext.ex;              // the next item's expert: its maps are in the descriptor cache when its copies start
+                    if (GATEUP) { tma_prefetch_map(&en->gate); tma_prefetch_map(&en->up); } else tma_prefetch_map(&en->down);
+                }
                 const int mb = item % MB;
                 const ExpertMaps *em = a.maps + tile.ex;
                 for (int sb = 0; sb < NSB && live; sb++, wcnt++) {

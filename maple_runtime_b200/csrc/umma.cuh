@@ -140,6 +140,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void *tmap,
                  ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 
+// pulls a tensor map into the descriptor cache ahead of its first use: a copy through a map that is not there waits for it, and the copies
+// queued behind it wait too
+__device__ __forceinline__ void tma_prefetch_map(const void *tmap) { asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory"); }
+
 // ---- asynchronous 16-byte copies global -> shared (gathered activation rows) -------------------------------------
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
