@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "kernels.h"
+#include "launch.cuh"
 #include "dev_math.cuh"
 
 extern "C" void k_count_add(long n);
@@ -174,7 +175,7 @@ static void launch(cudaStream_t st, const ExpertArgs *a) {
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(expert_mma_kernel<KCH, NBLK, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
     dim3 grid(GATEUP ? 8 : 16, a->max_tiles);
-    expert_mma_kernel<KCH, NBLK, GATEUP><<<grid, 128, smem, st>>>(*a);
+    launch_k(expert_mma_kernel<KCH, NBLK, GATEUP>, grid, 128, smem, st, *a);
     k_count_add(1);
 }
 extern "C" void k_gateup_mma(cudaStream_t st, const ExpertArgs *a, int tn) {
@@ -193,6 +194,6 @@ extern "C" void k_dense_mma(cudaStream_t st, const ExpertArgs *a, int rows) {
     const size_t smem = (size_t)8 * 4 * 32 * 64 + 32 * 8;
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(expert_mma_kernel<8, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr_done = true; }
-    expert_mma_kernel<8, 4, false><<<dim3(rows / 128, a->max_tiles), 128, smem, st>>>(*a);
+    launch_k(expert_mma_kernel<8, 4, false>, dim3(rows / 128, a->max_tiles), 128, smem, st, *a);
     k_count_add(1);
 }

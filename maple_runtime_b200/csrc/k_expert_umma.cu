@@ -38,6 +38,7 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include "kernels.h"
+#include "launch.cuh"
 #include "dev_math.cuh"
 #include "umma.cuh"
 
@@ -77,7 +78,6 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     static_assert(KB % 4 == 0, "blocks");
     const int MB = GATEUP ? 4 : (DENSE ? a.dense_mblocks : 8);      // 256-row blocks of the matrix (gate+up: 128 + 128)
     constexpr int NSB = KB / 4;
-    const int nitems = *a.ntiles * MB;
     volatile int *abortp = &sh->abort_flag;
 
     if (tid == 0) {
@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
     tc_fence_after();
     const uint32_t tb = sh->tmem_base;
     bool live = true;
+    const int nitems = *a.ntiles * MB;
 
     if (warp < 8) {
         // ---------------- decode: this warp's 32 rows of both halves, every second block, from the shared-memory ring ----------------
@@ -427,7 +428,7 @@ static void launch(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) {
         int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         cudaFuncSetAttribute(expert_umma_kernel<KB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
-    expert_umma_kernel<KB, MODE><<<sms, 640, smem, st>>>(*a, *bmap);
+    launch_k(expert_umma_kernel<KB, MODE>, sms, 640, smem, st, *a, *bmap);
     k_count_add(1);
 }
 extern "C" void k_gateup_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap) { if (a->max_tiles > 0) launch<16, 0>(st, a, bmap); }
@@ -449,6 +450,6 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t *__restri
 }
 extern "C" void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np) {
     if (np <= 0) return;
-    gather_rows_kernel<<<(np + 7) / 8, 256, 0, st>>>(src, rows, dst, np);
+    launch_k(gather_rows_kernel, (np + 7) / 8, 256, 0, st, src, rows, dst, np);
     k_count_add(1);
 }

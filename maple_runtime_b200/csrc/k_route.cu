@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include "kernels.h"
+#include "launch.cuh"
 #include "dev_math.cuh"
 #include "topk.cuh"
 
@@ -104,15 +105,15 @@ __global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict_
 }
 extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL, NULL, NULL); g_launches++;
+    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)NULL, (float *)NULL); g_launches++;
 }
 extern "C" void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, hS, NULL, NULL); g_launches++;
+    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, hS, (__half *)NULL, (float *)NULL); g_launches++;
 }
 extern "C" void k_norm_prep_split(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, void *hA, float *hnorm, int nb) {
     if (nb <= 0) return;
-    norm_prep_kernel<<<nb, 256, 0, st>>>(x, w, hn, q, qs, qsum, NULL, (__half *)hA, hnorm); g_launches++;
+    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)hA, hnorm); g_launches++;
 }
 
 // (Router logits live in k_router_tile.cu.)
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(256) topk_kernel(const float *__restrict__ log
 }
 extern "C" void k_topk(cudaStream_t st, const float *logits, int *top, float *topw, int nb) {
     if (nb <= 0) return;
-    topk_kernel<<<(nb + 7) / 8, 256, 0, st>>>(logits, top, topw, nb); g_launches++;
+    launch_k(topk_kernel, (nb + 7) / 8, 256, 0, st, logits, top, topw, nb); g_launches++;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -154,6 +155,10 @@ extern "C" void k_topk(cudaStream_t st, const float *logits, int *top, float *to
 //             word; UTOK, UW, the slot of every (token, choice), and tp = the token's eight slots sorted ascending (pair index
 //             order = expert order)
 // ------------------------------------------------------------------------------------------------------------
+__global__ void zero_words_kernel(unsigned *__restrict__ p, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = 0u;
+}
 __global__ void group_mark_kernel(const int *__restrict__ top, unsigned *__restrict__ mask, int mask_words, int np) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= np) return;
@@ -296,18 +301,19 @@ static void launch_group_cta(cudaStream_t st, const GroupArgs *g) {
     const int smem = NEXP * (MAXTOK / 32) * 4 + MAXTOK * TOPK * 4 + NEXP * (MAXTOK / 32) * 2;
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(group_cta_kernel<MAXTOK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_done = true; }
-    group_cta_kernel<MAXTOK, NT><<<1, NT, smem, st>>>(*g);
+    launch_k(group_cta_kernel<MAXTOK, NT>, 1, NT, smem, st, *g);
 }
 extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
     if (g->nb <= 256) { launch_group_cta<256, 256>(st, g); g_launches++; return; }
     const int np = g->nb * TOPK;
-    cudaMemsetAsync(g->mask, 0, ((size_t)NEXP * g->mask_words + NEXP) * sizeof(unsigned), st);   // bit words + the 256 counters behind them
-    group_mark_kernel<<<(np + 255) / 256, 256, 0, st>>>(g->top, g->mask, g->mask_words, np);
-    group_place_kernel<<<(g->nb + 127) / 128, NEXP, 0, st>>>(g->mask, g->mask_words, g->top, g->topw, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
+    const int zw = NEXP * g->mask_words + NEXP;                                               // bit words + the 256 counters behind them
+    launch_k(zero_words_kernel, (zw + 1023) / 1024, 1024, 0, st, g->mask, zw);
+    launch_k(group_mark_kernel, (np + 255) / 256, 256, 0, st, g->top, g->mask, g->mask_words, np);
+    launch_k(group_place_kernel, (g->nb + 127) / 128, NEXP, 0, st, g->mask, g->mask_words, g->top, g->topw, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
                                                             g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b,
                                                             g->utok, g->uw, g->slot, g->uexp, g->tp, g->nb);
-    g_launches += 2;
+    g_launches += 3;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -338,7 +344,7 @@ __global__ void __launch_bounds__(256) actq_kernel(const float *__restrict__ act
 }
 extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs, int *aqsum, const int *np_dev, int np_max) {
     if (np_max <= 0) return;
-    actq_kernel<<<(np_max + 7) / 8, 256, 0, st>>>(act, aq, aqs, aqsum, np_max, np_dev); g_launches++;
+    launch_k(actq_kernel, (np_max + 7) / 8, 256, 0, st, act, aq, aqs, aqsum, np_max, np_dev); g_launches++;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -364,10 +370,10 @@ __device__ __forceinline__ float silu_mul_approx(float g, float u) {
 template <bool EXACT>
 __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
                                                          int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np, const int *__restrict__ np_dev) {
-    if (np_dev) np = min(np, *np_dev);
     __shared__ unsigned long long tab[32];
     if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
     __syncthreads();
+    if (np_dev) np = min(np, *np_dev);
     const int lane = threadIdx.x & 31, a = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (a >= np) return;
     const float4 *gr = reinterpret_cast<const float4 *>(gate + (size_t)a * FFN) + lane * 4;
@@ -425,8 +431,8 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
 }
 extern "C" void k_silu_quant(cudaStream_t st, const float *gate, const float *up, float *act, int8_t *aq, float *aqs, int *aqsum, int np, const int *np_dev) {
     if (np <= 0) return;
-    if (act) silu_quant_kernel<true><<<(np + 7) / 8, 256, 0, st>>>(gate, up, act, aq, aqs, aqsum, np, np_dev);
-    else silu_quant_kernel<false><<<(np + 7) / 8, 256, 0, st>>>(gate, up, NULL, aq, aqs, aqsum, np, np_dev);
+    if (act) launch_k(silu_quant_kernel<true>, (np + 7) / 8, 256, 0, st, gate, up, act, aq, aqs, aqsum, np, np_dev);
+    else launch_k(silu_quant_kernel<false>, (np + 7) / 8, 256, 0, st, gate, up, (float *)NULL, aq, aqs, aqsum, np, np_dev);
     g_launches++;
 }
 
@@ -449,5 +455,5 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
 }
 extern "C" void k_combine(cudaStream_t st, const float *down, const float *uw, const int *tp, const float *init, float *out, int nb) {
     if (nb <= 0) return;
-    combine_kernel<<<(nb * 512 + 255) / 256, 256, 0, st>>>(down, uw, tp, init, out, nb); g_launches++;
+    launch_k(combine_kernel, (nb * 512 + 255) / 256, 256, 0, st, down, uw, tp, init, out, nb); g_launches++;
 }

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "kernels.h"
+#include "launch.cuh"
 #include "umma.cuh"
 
 #define HID 2048
@@ -170,8 +171,8 @@ static void launch_tile(cudaStream_t st, const void *router_t, const float *hn, 
     static bool attr_done = false;
     if (!attr_done) { cudaFuncSetAttribute(router_tile_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, RP_SMEM); attr_done = true; }
     const int tiles = (nb + 4 * TT - 1) / (4 * TT);
-    router_pack_h_kernel<<<tiles * 64, 256, 0, st>>>(hn, (float4 *)hT, nb, TT);
-    router_tile_kernel<TT><<<dim3(NEXP / RP_EXP, tiles), 256, RP_SMEM, st>>>((const uint8_t *)router_t, (const uint8_t *)hT, bias, logits, nb, err);
+    launch_k(router_pack_h_kernel, tiles * 64, 256, 0, st, hn, (float4 *)hT, nb, TT);
+    launch_k(router_tile_kernel<TT>, dim3(NEXP / RP_EXP, tiles), 256, RP_SMEM, st, (const uint8_t *)router_t, (const uint8_t *)hT, bias, logits, nb, err);
 }
 // A thread's tile is tt tokens x 16 experts, a CTA's 4*tt tokens x 128 experts; tt in 4..8 is chosen so that the CTAs fill whole
 // waves of the SMs with the least arithmetic per wave (2048 tokens: tt = 7, 148 CTAs).  hT must hold ceil(nb/16) * 256 KB.
@@ -281,9 +282,9 @@ extern "C" void k_router_logits_small(cudaStream_t st, const void *router_s, con
         cudaFuncSetAttribute(router_small_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB);
         cudaFuncSetAttribute(router_small_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_HB + RS_WB); attr_done = true;
     }
-    if (!relaid) router_pack_h_small_kernel<<<nb * 2, 256, 0, st>>>(hn, (float4 *)hS, nb);
+    if (!relaid) launch_k(router_pack_h_small_kernel, nb * 2, 256, 0, st, hn, (float4 *)hS, nb);
     const dim3 grid(NEXP / RS_EXP, (nb + RS_TOK - 1) / RS_TOK);
-    if (g_step_order && nb == 1) router_small_kernel<true><<<grid, 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
-    else router_small_kernel<false><<<grid, 256, RS_HB + RS_WB, st>>>((const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
+    if (g_step_order && nb == 1) launch_k(router_small_kernel<true>, grid, 256, RS_HB + RS_WB, st, (const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
+    else launch_k(router_small_kernel<false>, grid, 256, RS_HB + RS_WB, st, (const uint8_t *)router_s, (const uint8_t *)hS, bias, logits, nb, err);
     k_count_add(relaid ? 1 : 2);
 }

@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include "kernels.h"
+#include "launch.cuh"
 #include "umma.cuh"
 #include "topk.cuh"
 
@@ -79,7 +80,7 @@ struct RuBars { uint64_t full[RU_STAGES], empty[RU_STAGES], acc; uint32_t tmem_b
 // grid (RU_KS, token tiles of 128).  Warp 0: TMA (one lane), warp 1: tensor-memory allocation and MMA issue, warps 2-5: epilogue.
 // part [RU_KS][ntok_cap][256] fp32 receives the partial sums.
 __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_constant__ TMap amap, const __grid_constant__ TMap wmap,
-                                                             float *__restrict__ part, int nb, int ntok_cap, int *err) {
+                                                             float *__restrict__ part, int nb, int ntok_cap, int *err, int *__restrict__ nflagged) {
     extern __shared__ __align__(1024) uint8_t ru_raw[];
     uint8_t *ring = (uint8_t *)(((uintptr_t)ru_raw + 1023) & ~(uintptr_t)1023);
     __shared__ RuBars sh;
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tb = sh.tmem_base;
+    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) *nflagged = 0;      // the selection kernel counts its flagged tokens from zero
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < RU_KBLK; kb++) {
@@ -288,9 +290,8 @@ extern "C" void k_router_tensor(cudaStream_t st, const RouterTensorArgs *r) {
     static bool attr_done = false;
     const int smem = RU_STAGES * RU_STAGE_BYTES + 1024;
     if (!attr_done) { cudaFuncSetAttribute(router_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_done = true; }
-    cudaMemsetAsync(r->nflagged, 0, 4, st);
-    router_umma_kernel<<<dim3(RU_KS, (r->nb + 127) / 128), 192, smem, st>>>(r->amap, r->wmap, r->part, r->nb, r->ntok_cap, r->err);
-    router_select_kernel<<<(r->nb + 7) / 8, 256, 0, st>>>(r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, (const uint8_t *)r->router_s, r->nb);
-    router_fix_kernel<<<dim3(8, 74), 256, 0, st>>>((const uint8_t *)r->router_s, r->hn, r->bias, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->done, r->nb);
+    launch_k(router_umma_kernel, dim3(RU_KS, (r->nb + 127) / 128), 192, smem, st, r->amap, r->wmap, r->part, r->nb, r->ntok_cap, r->err, r->nflagged);
+    launch_k(router_select_kernel, (r->nb + 7) / 8, 256, 0, st, r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, (const uint8_t *)r->router_s, r->nb);
+    launch_k(router_fix_kernel, dim3(8, 74), 256, 0, st, (const uint8_t *)r->router_s, r->hn, r->bias, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->done, r->nb);
     k_count_add(3);
 }

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "kernels.h"
+#include "launch.cuh"
 
 extern "C" void k_count_add(long n);
 #define HID 2048
@@ -95,7 +96,7 @@ extern "C" void k_combine_wire(cudaStream_t st, uint8_t *wire, int np_cap, const
     int per = (nb + groups - 1) / groups; if (per < CW_WARPS) per = CW_WARPS;
     if (per > CW_MAXTOK) per = CW_MAXTOK;                                  /* more tokens than one wave holds: more groups */
     groups = (nb + per - 1) / per;
-    combine_wire_kernel<<<dim3(HID / CW_ROWS, groups), CW_WARPS * 32, smem, st>>>(wire, np_cap, dsp, uw, tp, init, out, nb, per);
+    launch_k(combine_wire_kernel, dim3(HID / CW_ROWS, groups), CW_WARPS * 32, smem, st, wire, np_cap, dsp, uw, tp, init, out, nb, per);
     k_count_add(1);
 }
 
@@ -121,6 +122,6 @@ __global__ void __launch_bounds__(256) wire_decode_kernel(const uint8_t *__restr
 }
 extern "C" void k_wire_decode(cudaStream_t st, const uint8_t *wire, int np_cap, const float *const *dsp, float *down, int np) {
     if (np <= 0) return;
-    wire_decode_kernel<<<np, 256, 0, st>>>(wire, np_cap, dsp, down, np);
+    launch_k(wire_decode_kernel, np, 256, 0, st, wire, np_cap, dsp, down, np);
     k_count_add(1);
 }
