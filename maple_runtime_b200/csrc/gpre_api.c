@@ -348,14 +348,15 @@ static void fill_expert_args(ExpertArgs *a, const ExpertPtrs *tab, const ExpertM
     if (S.keep || use_umma(nb)) { a->gate = S.gate; a->up = S.up; }          /* the tensor-core GEMM always stores gate and up */
     if (S.keep) { a->gu_dots = S.gu_dots; a->dn_dots = S.dn_dots; }
 }
-static void run_group(int nb) {
-    GroupArgs g; memset(&g, 0, sizeof g);
+static void run_group_m(int nb, int marked) {
+    GroupArgs g; memset(&g, 0, sizeof g); g.marked = marked && nb > 256;
     g.top = S.top; g.topw = S.topw; g.nb = nb; g.mask = S.mask; g.mask_words = S.mask_words; g.nu = S.nu; g.ue = S.ue; g.estart = S.estart;
     g.ustart = S.ustart; g.utok = S.utok; g.slot = S.slot; g.tp = S.tp; g.uw = S.uw; g.ecnt = S.ecnt; g.uexp = S.uexp;
     g.tiles_a = S.tiles_a; g.tiles_b = S.tiles_b; g.ntiles_a = S.ntiles_a; g.ntiles_b = S.ntiles_b; g.tn_a = tile_tn(nb); g.tn_b = UMMA_TN;
     k_group(S.st, &g);
     if (use_umma(nb) && !S.ep_on) k_gather_rows(S.st, S.hq, S.utok, S.hq_sorted, nb * TOPK);   /* the permute: int8 rows into pair order for the TMA */
 }
+static void run_group(int nb) { run_group_m(nb, 0); }
 /* which: 1 gateup, 2 actq, 4 down; dsp: the down-scale pointers the tiles' expert indices name (the combine needs the same) */
 static void run_experts(const ExpertPtrs *tab, const ExpertMaps *maps, const float *const *dsp, const int *ue, int nb, int which) {
     ExpertArgs a; fill_expert_args(&a, tab, maps, ue, nb);
@@ -399,13 +400,15 @@ int gmoe_set_router(int mode) { if (mode < 0 || mode > 2) return fail("gmoe", "r
 static int tensor_router(int nb) { return S.router_mode == 2 || (S.router_mode == 0 && nb >= 512); }
 int gmoe_router_flagged(void) { int n = -1; if (S.ready) { cudaMemcpyAsync(&n, S.nflagged, 4, cudaMemcpyDeviceToHost, S.st); cudaStreamSynchronize(S.st); } return n; }
 /* logits, top-8 and weights on the tensor cores (needs the fp16 terms and norms that k_norm_prep_split left) */
-static void run_router_tensor(const LayerDev *l, const float *bias, int nb) {
+static void run_router_tensor_m(const LayerDev *l, const float *bias, int nb, int mark) {
     RouterTensorArgs r; memset(&r, 0, sizeof r);
     r.amap = S.amap; r.wmap = l->wmap; r.part = S.rpart; r.nb = nb; r.ntok_cap = S.maxtok; r.err = S.err;
     r.bias = bias; r.hnorm = S.hnorm; r.wnorm = l->wnorm; r.hn = S.hn; r.router_s = l->router_s;
     r.logits = S.logits; r.top = S.top; r.topw = S.topw; r.flagged = S.flagged; r.nflagged = S.nflagged; r.done = S.rdone;
+    if (mark && nb > 256) { r.mask = S.mask; r.mask_words = S.mask_words; }      /* the grouping's bits and counters come out of the routing kernels */
     k_router_tensor(S.st, &r);
 }
+static void run_router_tensor(const LayerDev *l, const float *bias, int nb) { run_router_tensor_m(l, bias, nb, 0); }
 /* norm + int8 of the layer's input; decode batches also get the router's layout in the same pass */
 static int run_norm(const float *x, const uint16_t *w, int nb) {
     if (tensor_router(nb)) { k_norm_prep_split(S.st, x, w, S.hn, S.hq, S.hqs, S.hqsum, S.hA, S.hnorm, nb); return 0; }
@@ -416,12 +419,13 @@ static int run_norm(const float *x, const uint16_t *w, int nb) {
 static void run_layer(int L, int nb, int norm, const float *bias) {
     LayerDev *l = &S.ly[L];
     prof_begin(0); const int relaid = run_norm(norm ? S.x : S.hn, norm ? l->post_ln : NULL, nb); prof_end(0);
-    if (tensor_router(nb)) { prof_begin(1); run_router_tensor(l, bias, nb); prof_end(1); }
+    const int tr = tensor_router(nb);
+    if (tr) { prof_begin(1); run_router_tensor_m(l, bias, nb, 1); prof_end(1); }
     else {
         prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
         prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     }
-    prof_begin(3); run_group(nb); prof_end(3);
+    prof_begin(3); run_group_m(nb, tr); prof_end(3);
     run_experts(l->tab, l->maps, (const float *const *)l->dsp, S.ue, nb, 7);
     prof_begin(7);
     if (norm) run_combine((const float *const *)l->dsp, nb, S.x, S.x); else run_combine((const float *const *)l->dsp, nb, NULL, S.y);
@@ -993,13 +997,14 @@ static int run_layer_ep(int L, int nb, const float *bias) {
     LayerDev *l = &S.ly[L];
     const int tn = tile_tn(nb), um = use_umma(nb);
     prof_begin(0); const int relaid = run_norm(S.x, l->post_ln, nb); prof_end(0);
-    if (tensor_router(nb)) { prof_begin(1); run_router_tensor(l, bias, nb); prof_end(1); }
+    const int tr = tensor_router(nb);
+    if (tr) { prof_begin(1); run_router_tensor_m(l, bias, nb, 1); prof_end(1); }
     else {
         prof_begin(1); run_router_relaid(l, bias, nb, relaid); prof_end(1);
         prof_begin(2); k_topk(S.st, S.logits, S.top, S.topw, nb); prof_end(2);
     }
     prof_begin(3);
-    run_group(nb);
+    run_group_m(nb, tr);
     EpPlanArgs p = {EP.all_cnt, EP.rank, EP.world, EP.dst_base, EP.nu_r, EP.ue_r, EP.ustart_r, EP.total, S.tiles_a, S.tiles_b, S.ntiles_a, S.ntiles_b, tn, UMMA_TN};
     EpXchArgs xc = {S.ecnt, (int *const *)EP.peer_dev[5], EP.xch, EP.epoch, EP.rank, EP.world, EP.timeout_ns, S.err};
     k_ep_plan(S.st, &p, &xc);

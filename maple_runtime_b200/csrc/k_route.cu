@@ -307,13 +307,16 @@ extern "C" void k_group(cudaStream_t st, const GroupArgs *g) {
     if (g->nb <= 0) return;
     if (g->nb <= 256) { launch_group_cta<256, 256>(st, g); g_launches++; return; }
     const int np = g->nb * TOPK;
-    const int zw = NEXP * g->mask_words + NEXP;                                               // bit words + the 256 counters behind them
-    launch_k(zero_words_kernel, (zw + 1023) / 1024, 1024, 0, st, g->mask, zw);
-    launch_k(group_mark_kernel, (np + 255) / 256, 256, 0, st, g->top, g->mask, g->mask_words, np);
+    if (!g->marked) {
+        const int zw = NEXP * g->mask_words + NEXP;                                           // bit words + the 256 counters behind them
+        launch_k(zero_words_kernel, (zw + 1023) / 1024, 1024, 0, st, g->mask, zw);
+        launch_k(group_mark_kernel, (np + 255) / 256, 256, 0, st, g->top, g->mask, g->mask_words, np);
+        g_launches += 2;
+    }
     launch_k(group_place_kernel, (g->nb + 127) / 128, NEXP, 0, st, g->mask, g->mask_words, g->top, g->topw, g->nu, g->ue, g->estart, g->ustart, g->ecnt,
                                                             g->tiles_a, g->ntiles_a, g->tn_a, g->tiles_b, g->ntiles_b, g->tn_b,
                                                             g->utok, g->uw, g->slot, g->uexp, g->tp, g->nb);
-    g_launches += 3;
+    g_launches += 1;
 }
 
 // ------------------------------------------------------------------------------------------------------------

@@ -80,7 +80,8 @@ struct RuBars { uint64_t full[RU_STAGES], empty[RU_STAGES], acc; uint32_t tmem_b
 // grid (RU_KS, token tiles of 128).  Warp 0: TMA (one lane), warp 1: tensor-memory allocation and MMA issue, warps 2-5: epilogue.
 // part [RU_KS][ntok_cap][256] fp32 receives the partial sums.
 __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_constant__ TMap amap, const __grid_constant__ TMap wmap,
-                                                             float *__restrict__ part, int nb, int ntok_cap, int *err, int *__restrict__ nflagged) {
+                                                             float *__restrict__ part, int nb, int ntok_cap, int *err, int *__restrict__ nflagged,
+                                                             unsigned *__restrict__ mask, int mask_n) {
     extern __shared__ __align__(1024) uint8_t ru_raw[];
     uint8_t *ring = (uint8_t *)(((uintptr_t)ru_raw + 1023) & ~(uintptr_t)1023);
     __shared__ RuBars sh;
@@ -97,6 +98,10 @@ __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_consta
     tc_fence_after();
     const uint32_t tb = sh.tmem_base;
     if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) *nflagged = 0;      // the selection kernel counts its flagged tokens from zero
+    if (mask) {     // and sets the grouping's bits and counters: cleared here, one word per thread
+        const int w = (blockIdx.y * gridDim.x + blockIdx.x) * 192 + tid;
+        for (int i = w; i < mask_n; i += gridDim.x * gridDim.y * 192) mask[i] = 0u;
+    }
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < RU_KBLK; kb++) {
@@ -162,7 +167,8 @@ __global__ void __launch_bounds__(192, 1) router_umma_kernel(const __grid_consta
 __global__ void __launch_bounds__(256) router_select_kernel(const float *__restrict__ part, int ntok_cap, const float *__restrict__ bias,
                                                             const float *__restrict__ hnorm, const float *__restrict__ wnorm,
                                                             float *__restrict__ logits, int *__restrict__ top, float *__restrict__ topw,
-                                                            int *__restrict__ flagged, int *__restrict__ nflagged, const uint8_t *__restrict__ router_s, int nb) {
+                                                            int *__restrict__ flagged, int *__restrict__ nflagged, const uint8_t *__restrict__ router_s,
+                                                            unsigned *__restrict__ mask, int mask_words, int nb) {
     {   // the flagged tokens' recomputation reads the layer's re-laid router rows (1 MB) right after this kernel: pull them into L2 now
         const unsigned line = blockIdx.x * 256u + threadIdx.x;
         if (line < NEXP * HID * 2 / 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(router_s + (size_t)line * 128));
@@ -230,7 +236,10 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float *__restr
     float tsum = 0.0f;
 #pragma unroll
     for (int k = 0; k < TOPK; k++) tsum += __shfl_sync(0xffffffffu, ek, k);
-    if (lane < TOPK) { top[b * TOPK + lane] = isel; topw[b * TOPK + lane] = ek / (tsum + 1e-20f); }
+    if (lane < TOPK) {
+        top[b * TOPK + lane] = isel; topw[b * TOPK + lane] = ek / (tsum + 1e-20f);
+        if (mask) { atomicOr(&mask[(size_t)(b >> 5) * NEXP + isel], 1u << (b & 31)); atomicAdd(&mask[(size_t)NEXP * mask_words + isel], 1u); }
+    }
 }
 
 // The flagged tokens over again as the reference computes them (maple.c:870-889, 117-121, 910-923).  grid (8 expert eighths, y): CTA
@@ -240,7 +249,8 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float *__restr
 // WS: the router rows re-laid as [expert][column / 32][lane j][4 steps] bf16 (k_router_pack_small, k_router_tile.cu).
 __global__ void __launch_bounds__(256) router_fix_kernel(const uint8_t *__restrict__ WS, const float *__restrict__ hn, const float *__restrict__ bias,
                                                          float *__restrict__ logits, int *__restrict__ top, float *__restrict__ topw,
-                                                         const int *__restrict__ flagged, const int *__restrict__ nflagged, int *__restrict__ done, int nb) {
+                                                         const int *__restrict__ flagged, const int *__restrict__ nflagged, int *__restrict__ done,
+                                                         unsigned *__restrict__ mask, int mask_words, int nb) {
     __shared__ __align__(16) float hrow[HID];
     __shared__ unsigned long long tab[32];
     __shared__ int s_last;
@@ -279,7 +289,10 @@ __global__ void __launch_bounds__(256) router_fix_kernel(const uint8_t *__restri
             float p[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
             int isel; float wsel, tsum;
             exact_topk_warp(p, lane, tab, isel, wsel, tsum);
-            if (lane < TOPK) { top[b * TOPK + lane] = isel; topw[b * TOPK + lane] = __fdiv_rn(wsel, __fadd_rn(tsum, 1e-20f)); }
+            if (lane < TOPK) {
+                top[b * TOPK + lane] = isel; topw[b * TOPK + lane] = __fdiv_rn(wsel, __fadd_rn(tsum, 1e-20f));
+                if (mask) { atomicOr(&mask[(size_t)(b >> 5) * NEXP + isel], 1u << (b & 31)); atomicAdd(&mask[(size_t)NEXP * mask_words + isel], 1u); }
+            }
             if (lane == 0) done[f] = 0;
         }
     }
@@ -290,8 +303,8 @@ extern "C" void k_router_tensor(cudaStream_t st, const RouterTensorArgs *r) {
     static bool attr_done = false;
     const int smem = RU_STAGES * RU_STAGE_BYTES + 1024;
     if (!attr_done) { cudaFuncSetAttribute(router_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_done = true; }
-    launch_k(router_umma_kernel, dim3(RU_KS, (r->nb + 127) / 128), 192, smem, st, r->amap, r->wmap, r->part, r->nb, r->ntok_cap, r->err, r->nflagged);
-    launch_k(router_select_kernel, (r->nb + 7) / 8, 256, 0, st, r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, (const uint8_t *)r->router_s, r->nb);
-    launch_k(router_fix_kernel, dim3(8, 74), 256, 0, st, (const uint8_t *)r->router_s, r->hn, r->bias, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->done, r->nb);
+    launch_k(router_umma_kernel, dim3(RU_KS, (r->nb + 127) / 128), 192, smem, st, r->amap, r->wmap, r->part, r->nb, r->ntok_cap, r->err, r->nflagged, r->mask, NEXP * r->mask_words + NEXP);
+    launch_k(router_select_kernel, (r->nb + 7) / 8, 256, 0, st, r->part, r->ntok_cap, r->bias, r->hnorm, r->wnorm, r->logits, r->top, r->topw, r->flagged, r->nflagged, (const uint8_t *)r->router_s, r->mask, r->mask_words, r->nb);
+    launch_k(router_fix_kernel, dim3(8, 74), 256, 0, st, (const uint8_t *)r->router_s, r->hn, r->bias, r->logits, r->top, r->topw, r->flagged, r->nflagged, r->done, r->mask, r->mask_words, r->nb);
     k_count_add(3);
 }

@@ -65,6 +65,7 @@ typedef struct {
     unsigned *mask;          /* [mask_words][256] bit words (bit b % 32 of word b / 32: token b chose the expert), then 256 counters */
     int mask_words;
     int *nu, *ue, *estart, *ustart, *utok, *slot, *tp; float *uw;
+    int marked;              /* 1: the routing kernels have already set the bits and counters in mask */
     int *ecnt, *uexp;        /* optional: pairs per expert [256], expert of every pair [np] (expert parallel) */
     MoeTile *tiles_a, *tiles_b; int *ntiles_a, *ntiles_b; int tn_a, tn_b;   /* two tile lists: sizes tn_a and tn_b */
 } GroupArgs;
@@ -107,6 +108,7 @@ typedef struct {
     const void *router_s;    /* the rows re-laid by k_router_pack_small: the exact recomputation reads them */
     float *logits; int *top; float *topw;
     int *flagged, *nflagged; /* [nb], [1]: tokens that took the exact path (left for inspection) */
+    unsigned *mask; int mask_words;   /* optional: the grouping's bit words and counters (GroupArgs.mask): cleared and filled here, k_group then runs with marked = 1 */
     int *done;               /* [nb] counters, zero between calls */
 } RouterTensorArgs;
 void k_router_w16(cudaStream_t st, const uint16_t *router, void *w16, float *wnorm);

@@ -61,7 +61,7 @@ extern "C" int gmoe_group_noalloc(const int *top, const float *topw, int nb, int
     }
     NaScratch *s = g_na_dev[dev];
     GroupArgs g;
-    g.top = top; g.topw = topw; g.nb = nb;
+    g.top = top; g.topw = topw; g.nb = nb; g.marked = 0;
     g.mask = s->mask; g.mask_words = (nb + 31) / 32;
     g.nu = nu; g.ue = ue; g.estart = s->estart; g.ustart = ustart; g.utok = utok; g.slot = s->slot; g.tp = tp; g.uw = uw;
     g.ecnt = NULL; g.uexp = NULL;
