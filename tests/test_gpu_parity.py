@@ -419,3 +419,45 @@ def test_fast_silu_int8_equals_exact_variant(layers, oracle):
     for a in list(range(601, P, 997)) + [150, 270, 350, 450, 550]:     # the exact variant itself against the oracle's prep of its act row (rows of ordinary magnitude)
         q, qs, qsum = oracle.prep(want["act"][a])
         assert np.array_equal(q, want["aq"][a]) and np.float32(qs).tobytes() == want["aqs"][a].tobytes() and qsum == want["aqsum"][a]
+
+
+@pytest.mark.parametrize("nb,stream", [(2048, 801), (700, 802)])
+def test_timed_path_int8_rows_equal_the_kept_stages_path(nb, stream, layers, oracle, weights):
+    """Without kept stages the tcgen05 gate+up kernel stores SiLU(gate) * up evaluated with the hardware's approximate exponential and
+    the int8 step computes again, exactly, the elements where that could show (row maximum candidates, values next to a rounding
+    boundary).  Its int8 rows, scales and sums must be the bits of the kept-stages path (every element with the libm-equal expf,
+    which other tests pin to the oracle), on ordinary tokens and on tokens built to stress the fall-backs: zero rows (512 equal
+    products), tiny and huge magnitudes (underflowing products; gate clamped at 7 and up at +-7, exp(-g) up to overflow), repeated
+    and negated tokens; a sample of rows also against the oracle's prep (maple.c:184-194, 825-832)."""
+    g = layers
+    P = nb * 8
+    hn = weights.hidden(stream, nb)
+    hn[3] = 0.0; hn[40] = 0.0
+    hn[50:80] *= np.float32(1e-20); hn[80:100] *= np.float32(1e-30); hn[100:110] *= np.float32(1e-37)
+    hn[110:160] *= np.float32(30.0); hn[160:200] *= np.float32(300.0); hn[200:220] *= np.float32(1e6)
+    hn[220] = hn[221]; hn[222] = -hn[223]
+    hn[230:260, 1:] = 0.0                                   # one non-zero hidden value: dots are +-q or 0, many equal products
+    out = {}
+    g.set_path(2)
+    try:
+        g.poke("hn", hn)
+        for name in ("prep", "router", "topk", "group"):
+            g.stage(name, 0, nb)
+        for keep in (True, False):
+            g.keep_stages(keep)
+            if not keep:
+                g.poke("aq", np.zeros((P, 512), np.int8))
+            g.stage("gateup", 0, nb); g.stage("actq", 0, nb)
+            out[keep] = {k: g.peek(k, nb).copy() for k in (("aq", "aqs", "aqsum", "act") if keep else ("aq", "aqs", "aqsum"))}
+    finally:
+        g.keep_stages(True); g.set_path(0)
+    want, got = out[True], out[False]
+    bad = np.argwhere(got["aq"].reshape(P, 512) != want["aq"].reshape(P, 512))
+    assert bad.size == 0, f"{len(bad)} int8 values differ, first at {bad[:3].tolist()}"
+    assert same_bits(got["aqs"], want["aqs"]) and np.array_equal(got["aqsum"], want["aqsum"])
+    act = want["act"].reshape(P, 512)
+    for a in range(5, P, 1499):                              # the kept-stages path itself against the oracle's prep of its act row
+        if float(np.abs(act[a]).max()) < 1e-30:
+            continue
+        q, qs, qsum = oracle.prep(act[a])
+        assert np.array_equal(q, want["aq"].reshape(P, 512)[a]) and np.float32(qs).tobytes() == want["aqs"].reshape(P)[a].tobytes() and qsum == want["aqsum"].reshape(P)[a]
