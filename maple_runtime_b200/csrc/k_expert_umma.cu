@@ -241,12 +241,19 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
             }
         };
         if (blockIdx.x < nitems) header_load(t1);
+        // the row scales of an item are read while the item before it is worked on (the pointer table they hang off has arrived by then)
+        float s0n = 0.0f, s1n = 0.0f;
+        auto scales_load = [&](const ExpertPtrs &e, const int it) {
+            const int r = GATEUP ? (it % MB) * 128 + row : (it % MB) * 256 + 2 * row;
+            s0n = GATEUP ? e.gs[r] : (DENSE ? e.ds[r] : 0.0f); s1n = GATEUP ? e.us[r] : (DENSE ? e.ds[r + 1] : 0.0f);
+        };
+        if (blockIdx.x < nitems) scales_load(ep1, blockIdx.x);
         for (int item = blockIdx.x; item < nitems && live; item += stride, icnt++) {
             const MoeTile tile = t1; const ExpertPtrs ep = ep1;
             const int mb = item % MB, cnt = tile.cnt, N = (cnt + 15) & ~15;
             const uint32_t buf = icnt % NACC;
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + 2 * row;      // down: half 0 holds row r0, half 1 row r0 + 1
-            const float s0 = GATEUP ? ep.gs[r0] : (DENSE ? ep.ds[r0] : 0.0f), s1 = GATEUP ? ep.us[r0] : (DENSE ? ep.ds[r0 + 1] : 0.0f);
+            const float s0 = s0n, s1 = s1n;
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < HN; i++) {
@@ -408,6 +415,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
                     piece(c0, v0, v1);
                 }
             }
+            if (item + stride < nitems) scales_load(ep1, item + stride);
         }
     }
     tc_fence_before();

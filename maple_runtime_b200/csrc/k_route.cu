@@ -352,7 +352,8 @@ extern "C" void k_actq(cudaStream_t st, const float *act, int8_t *aq, float *aqs
 
 // ------------------------------------------------------------------------------------------------------------
 // SiLU*up + int8 in one pass (maple.c:825-832) for the tensor-core path, whose GEMM stores gate and up: one warp per
-// pair, 16 values per lane.  act (optional) receives the fp32 activations for stage comparisons.
+// pair, 16 values per lane: columns 128 i + 4 lane .. + 3 for i = 0..3, so that every load and store instruction of the warp covers
+// one contiguous run of the row.  act (optional) receives the fp32 activations for stage comparisons.
 //
 // The int8 row, its scale and its sum are the reference's bits in both variants.  EXACT evaluates every element with the libm-equal
 // expf in double (dev_math.cuh).  The other variant evaluates act ~ g / (1 + 2^(-g log2 e)) u with the hardware's approximate
@@ -371,7 +372,7 @@ __device__ __forceinline__ float silu_mul_approx(float g, float u) {
     return g * r * u;
 }
 template <bool EXACT>
-__global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
+__global__ void __launch_bounds__(256, 4) silu_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ act,
                                                          int8_t *__restrict__ aq, float *__restrict__ aqs, int *__restrict__ aqsum, int np, const int *__restrict__ np_dev) {
     __shared__ unsigned long long tab[32];
     if (threadIdx.x < 32) tab[threadIdx.x] = DEV_EXP_TAB[threadIdx.x];
@@ -379,12 +380,12 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
     if (np_dev) np = min(np, *np_dev);
     const int lane = threadIdx.x & 31, a = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (a >= np) return;
-    const float4 *gr = reinterpret_cast<const float4 *>(gate + (size_t)a * FFN) + lane * 4;
-    const float4 *ur = reinterpret_cast<const float4 *>(up + (size_t)a * FFN) + lane * 4;
+    const float4 *gr = reinterpret_cast<const float4 *>(gate + (size_t)a * FFN) + lane;
+    const float4 *ur = reinterpret_cast<const float4 *>(up + (size_t)a * FFN) + lane;
     float gv[16], uv[16], v[16];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const float4 g = gr[i], u = ur[i];
+        const float4 g = gr[32 * i], u = ur[32 * i];
         gv[4 * i] = g.x; gv[4 * i + 1] = g.y; gv[4 * i + 2] = g.z; gv[4 * i + 3] = g.w;
         uv[4 * i] = u.x; uv[4 * i + 1] = u.y; uv[4 * i + 2] = u.z; uv[4 * i + 3] = u.w;
     }
@@ -393,9 +394,9 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
 #pragma unroll
         for (int i = 0; i < 16; i++) { v[i] = dev_silu_mul_tab(gv[i], uv[i], tab); mx = fmaxf(mx, fabsf(v[i])); }
         if (act) {
-            float4 *o = reinterpret_cast<float4 *>(act + (size_t)a * FFN) + lane * 4;
+            float4 *o = reinterpret_cast<float4 *>(act + (size_t)a * FFN) + lane;
 #pragma unroll
-            for (int i = 0; i < 4; i++) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            for (int i = 0; i < 4; i++) o[32 * i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -427,7 +428,8 @@ __global__ void __launch_bounds__(256) silu_quant_kernel(const float *__restrict
             tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3));
         }
     }
-    reinterpret_cast<uint4 *>(aq + (size_t)a * FFN)[lane] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+#pragma unroll
+    for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(aq + (size_t)a * FFN)[32 * i + lane] = pk[i];
 #pragma unroll
     for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     if (lane == 0) { aqs[a] = s; aqsum[a] = tot; }
