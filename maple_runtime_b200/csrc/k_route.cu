@@ -23,7 +23,9 @@ extern "C" void k_count_add(long n) { g_launches += n; }
 #define FFN 512
 
 // ------------------------------------------------------------------------------------------------------------
-// RMSNorm (maple.c:398-402) + prep (maple.c:184-194), one CTA of 256 threads per token, 8 columns per thread.
+// RMSNorm (maple.c:398-402) + prep (maple.c:184-194), one warp per token: lane l holds columns 128 i + 4 l .. + 3 for i = 0..15 (every
+// load and store instruction of the warp covers one contiguous run of the row, all sixteen loads are in flight together, and the three
+// reductions are shuffles: no block-wide barrier).  WPC warps (tokens) per CTA: 8 for chunks, 1 for decode batches (more CTAs).
 // w == NULL: x is already normalised (hn = x, not rewritten when hn == x).
 // The sum of squares is accumulated in double like the reference; the tree order differs from its left-to-right
 // order only below double precision, which the conversion to float absorbs.
@@ -31,89 +33,94 @@ extern "C" void k_count_add(long n) { g_launches += n; }
 // hS != NULL: the normalised row is also stored as the decode router wants it, [column / 32][lane j][4 steps] (k_router_tile.cu).
 // hA != NULL: the normalised row is also stored as two fp16 terms, hi = fp16(h) in columns 0..2047 and lo = fp16(h - hi) in columns
 // 2048..4095 of a 4096-column row (the tensor-core router's A operand, k_router_umma.cu), and its Euclidean norm goes to hnorm.
-__global__ void __launch_bounds__(256) norm_prep_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w,
-                                                        float *__restrict__ hn, int8_t *__restrict__ q,
-                                                        float *__restrict__ qs, int *__restrict__ qsum, float *__restrict__ hS,
-                                                        __half *__restrict__ hA, float *__restrict__ hnorm) {
-    __shared__ double sd[8];
-    __shared__ float sf[8], sn[8];
-    __shared__ int si[8];
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)b * HID) + tid * 2;
-    float4 v0 = xr[0], v1 = xr[1];
-    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+template <int WPC>
+__global__ void __launch_bounds__(WPC * 32) norm_prep_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w,
+                                                             float *__restrict__ hn, int8_t *__restrict__ q,
+                                                             float *__restrict__ qs, int *__restrict__ qsum, float *__restrict__ hS,
+                                                             __half *__restrict__ hA, float *__restrict__ hnorm, int nb) {
+    const int lane = threadIdx.x & 31, b = blockIdx.x * WPC + (threadIdx.x >> 5);
+    if (b >= nb) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)b * HID) + lane;
+    float4 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = xr[32 * i];
     if (w) {
+        uint2 wr[16];                                            // 4 bf16 each
+#pragma unroll
+        for (int i = 0; i < 16; i++) wr[i] = reinterpret_cast<const uint2 *>(w)[32 * i + lane];
         double ss = 0.0;
 #pragma unroll
-        for (int i = 0; i < 8; i++) ss += (double)v[i] * (double)v[i];
+        for (int i = 0; i < 16; i++) ss += (double)v[i].x * (double)v[i].x + (double)v[i].y * (double)v[i].y + ((double)v[i].z * (double)v[i].z + (double)v[i].w * (double)v[i].w);
 #pragma unroll
         for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) sd[wid] = ss;
-        __syncthreads();
-        double tot = ((sd[0] + sd[1]) + (sd[2] + sd[3])) + ((sd[4] + sd[5]) + (sd[6] + sd[7]));
-        float k = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)HID), 1e-6f)));
-        const uint4 wr = reinterpret_cast<const uint4 *>(w)[tid];   // 8 bf16
-        const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
+        const float k = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(ss / (double)HID), 1e-6f)));
+        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + lane;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float wf = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xFFFF0000u) : (ww[i >> 1] << 16));
-            v[i] = __fmul_rn(__fmul_rn(v[i], k), wf);
+        for (int i = 0; i < 16; i++) {
+            v[i].x = __fmul_rn(__fmul_rn(v[i].x, k), __uint_as_float(wr[i].x << 16)); v[i].y = __fmul_rn(__fmul_rn(v[i].y, k), __uint_as_float(wr[i].x & 0xFFFF0000u));
+            v[i].z = __fmul_rn(__fmul_rn(v[i].z, k), __uint_as_float(wr[i].y << 16)); v[i].w = __fmul_rn(__fmul_rn(v[i].w, k), __uint_as_float(wr[i].y & 0xFFFF0000u));
+            hr[32 * i] = v[i];
         }
-        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + tid * 2;
-        hr[0] = make_float4(v[0], v[1], v[2], v[3]); hr[1] = make_float4(v[4], v[5], v[6], v[7]);
     } else if (hn != x) {
-        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + tid * 2;
-        hr[0] = v0; hr[1] = v1;
-    }
-    if (hS) {      // thread tid holds step i = tid of all eight lanes j: granule (i / 4, j), slot i % 4
-        float *d = hS + (size_t)b * HID + (tid >> 2) * 32 + (tid & 3);
+        float4 *hr = reinterpret_cast<float4 *>(hn + (size_t)b * HID) + lane;
 #pragma unroll
-        for (int j = 0; j < 8; j++) d[j * 4] = v[j];
+        for (int i = 0; i < 16; i++) hr[32 * i] = v[i];
+    }
+    if (hS) {      // column c goes to (c / 32) * 32 + (c % 8) * 4 + (c / 8) % 4: granule (step / 4, lane j), slot step % 4
+        float *d = hS + (size_t)b * HID;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int c = 128 * i + 4 * lane;                    // c % 8 is 0 or 4
+            float *p = d + (c >> 5) * 32 + (c & 7) * 4 + ((c >> 3) & 3);
+            p[0] = v[i].x; p[4] = v[i].y; p[8] = v[i].z; p[12] = v[i].w;
+        }
     }
     float mx = 0.0f, n2 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+    for (int i = 0; i < 16; i++) mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
     if (hA) {
-        __align__(16) __half hi[8], lo[8];
+        uint2 *hi_row = reinterpret_cast<uint2 *>(hA + (size_t)b * (2 * HID)) + lane, *lo_row = hi_row + HID / 4;
 #pragma unroll
-        for (int i = 0; i < 8; i++) { hi[i] = __float2half_rn(v[i]); lo[i] = __float2half_rn(v[i] - __half2float(hi[i])); n2 = fmaf(v[i], v[i], n2); }
-        __half *row = hA + (size_t)b * (2 * HID) + tid * 8;
-        *reinterpret_cast<uint4 *>(row) = *reinterpret_cast<const uint4 *>(hi);
-        *reinterpret_cast<uint4 *>(row + HID) = *reinterpret_cast<const uint4 *>(lo);
+        for (int i = 0; i < 16; i++) {
+            const float f[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            __align__(8) __half hi[4], lo[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) { hi[k] = __float2half_rn(f[k]); lo[k] = __float2half_rn(f[k] - __half2float(hi[k])); n2 = fmaf(f[k], f[k], n2); }
+            hi_row[32 * i] = *reinterpret_cast<const uint2 *>(hi); lo_row[32 * i] = *reinterpret_cast<const uint2 *>(lo);
+        }
 #pragma unroll
         for (int o = 16; o; o >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, o);
+        if (lane == 0) hnorm[b] = sqrtf(n2);
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) { sf[wid] = mx; sn[wid] = n2; }
-    __syncthreads();
-    if (hA && tid == 0) hnorm[b] = sqrtf(((sn[0] + sn[1]) + (sn[2] + sn[3])) + ((sn[4] + sn[5]) + (sn[6] + sn[7])));
-    mx = fmaxf(fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3])), fmaxf(fmaxf(sf[4], sf[5]), fmaxf(sf[6], sf[7])));
     const float s = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : 1.0f, inv = __fdiv_rn(1.0f, s);
-    int tot = 0; uint32_t pk[2] = {0, 0};
+    int tot = 0;
+    uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)b * HID) + lane;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        int qi = __float2int_rn(__fmul_rn(v[i], inv));
-        tot += qi; pk[i >> 2] |= (uint32_t)(qi & 0xFF) << (8 * (i & 3));
+    for (int i = 0; i < 16; i++) {
+        const int q0 = __float2int_rn(__fmul_rn(v[i].x, inv)), q1 = __float2int_rn(__fmul_rn(v[i].y, inv)), q2 = __float2int_rn(__fmul_rn(v[i].z, inv)), q3 = __float2int_rn(__fmul_rn(v[i].w, inv));
+        tot += (q0 + q1) + (q2 + q3);
+        qr[32 * i] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
     }
-    reinterpret_cast<uint2 *>(q + (size_t)b * HID)[tid] = make_uint2(pk[0], pk[1]);
 #pragma unroll
     for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-    if (lane == 0) si[wid] = tot;
-    __syncthreads();
-    if (tid == 0) { qs[b] = s; qsum[b] = si[0] + si[1] + si[2] + si[3] + si[4] + si[5] + si[6] + si[7]; }
+    if (lane == 0) { qs[b] = s; qsum[b] = tot; }
+}
+static void norm_launch(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, __half *hA, float *hnorm, int nb) {
+    if (nb <= 0) return;
+    if (nb > 256) launch_k(norm_prep_kernel<8>, (nb + 7) / 8, 256, 0, st, x, w, hn, q, qs, qsum, hS, hA, hnorm, nb);
+    else launch_k(norm_prep_kernel<1>, nb, 32, 0, st, x, w, hn, q, qs, qsum, hS, hA, hnorm, nb);
+    g_launches++;
 }
 extern "C" void k_norm_prep(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, int nb) {
-    if (nb <= 0) return;
-    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)NULL, (float *)NULL); g_launches++;
+    norm_launch(st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)NULL, (float *)NULL, nb);
 }
 extern "C" void k_norm_prep_relaid(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, float *hS, int nb) {
-    if (nb <= 0) return;
-    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, hS, (__half *)NULL, (float *)NULL); g_launches++;
+    norm_launch(st, x, w, hn, q, qs, qsum, hS, (__half *)NULL, (float *)NULL, nb);
 }
 extern "C" void k_norm_prep_split(cudaStream_t st, const float *x, const uint16_t *w, float *hn, int8_t *q, float *qs, int *qsum, void *hA, float *hnorm, int nb) {
-    if (nb <= 0) return;
-    launch_k(norm_prep_kernel, nb, 256, 0, st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)hA, hnorm); g_launches++;
+    norm_launch(st, x, w, hn, q, qs, qsum, (float *)NULL, (__half *)hA, hnorm, nb);
 }
 
 // (Router logits live in k_router_tile.cu.)
