@@ -7,8 +7,9 @@
 One step = one 2048-token chunk through all 24 layers on each GPU.  `value` is tokens/s with the chunk already in
 HBM (device-timed, max over ranks); `e2e` is the same through the host-buffer entry point gmoe_forward (pinned host
 input copied in, result copied out, inside the timed region).  `roofline` describes the dominant kernel (the grouped
-gate+up GEMM), timed with CUDA events around its launches in a pass of its own, against the tcgen05 kind::i8 rate measured
-on this GPU in the same run.  `e2e_gpre_moe` is the same chunk through 24 calls of the reference-signature gpre_moe (host
+gate+up GEMM), timed with CUDA events around its launches in a pass of its own: its algorithmic bytes against the measured copy
+bandwidth (the roof that binds at 64 pairs per expert), and its integer operations against the tcgen05 kind::i8 rate measured on
+this GPU in the same run (`roofline.tensor`).  `e2e_gpre_moe` is the same chunk through 24 calls of the reference-signature gpre_moe (host
 grouping tables, host buffers: the call an unmodified maple.c makes).  `parity_check` compares two layers of the chunk with
 the reference (oracle/_ref) before anything is timed.  `cpu_baseline` times the reference's own CPU code on a bounded sample
 on this host; `--impl reference` runs that code over the whole 24-layer stack.  `decode` repeats the measurement for the
@@ -361,12 +362,22 @@ def main():
     gu_t = float(secs[4]) / max(int(nlaunch[4]), 1)          # stage 4 is one launch per layer: the grouped gate+up GEMM
     gu_tops = GU_OPS_PER_PAIR * NB * 8 / gu_t / 1e12
     traffic, traffic_src = profiled_traffic("gate_up")
-    roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary, tcgen05 kind::i8)", "bound": "tensor", "achieved": gu_tops, "peak": i8_peak, "unit": "TOP/s (int8)",
-                "frac": gu_tops / i8_peak if i8_peak > 0 else None, "traffic": traffic, "traffic_unit": "bytes per launch",
+    # Which roof binds: the kernel's algorithmic bytes over the measured copy bandwidth against its integer operations over the measured
+    # kind::i8 rate.  Per pair 2048 B of int8 activations in and 2 x 512 fp32 values out; per expert its gate and up codes and row scales
+    # once (every expert is used at this size).  At 64 pairs per expert that is 291 operations per byte, below the machine balance
+    # (~700), so the HBM roof is the binding one; the tensor roof is reported beside it.
+    gu_bytes = NB * 8 * (2048 + 2 * 512 * 4) + 256 * 2 * 264192
+    gu_gbs = gu_bytes / gu_t / 1e9
+    t_hbm, t_tensor = gu_bytes / (pk["hbm_gbs"] * 1e9), (GU_OPS_PER_PAIR * NB * 8 / (i8_peak * 1e12) if i8_peak > 0 else 0.0)
+    roofline = {"kernel": "grouped gate+up GEMM (int8 x ternary, tcgen05 kind::i8)", "bound": "hbm" if t_hbm >= t_tensor else "tensor",
+                "achieved": gu_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gu_gbs / pk["hbm_gbs"], "peak_source": pk["src"],
+                "algorithmic_bytes_per_launch": gu_bytes, "roof_us": {"hbm": t_hbm * 1e6, "tensor": t_tensor * 1e6},
+                "traffic": traffic, "traffic_unit": "bytes per launch",
                 "traffic_note": f"dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the ncu summary profiles/{traffic_src}" if traffic else "no ncu summary of this kernel under profiles/",
                 "launches_timed": int(nlaunch[4]), "avg_launch_us": gu_t * 1e6,
-                "peak_note": "tcgen05.mma kind::i8, M=128 N=256 K=32, operands resident in shared memory, one CTA per SM, measured in this run with CUDA events (gmoe_i8_peak)",
-                "frac_of_2x_bf16_burst": gu_tops / (2.0 * pk["bf16_tflops"]), "frac_of_2x_bf16_sustained": gu_tops / (2.0 * pk["bf16_tflops_sustained"]),
+                "tensor": {"achieved": gu_tops, "peak": i8_peak, "unit": "TOP/s (int8)", "frac": gu_tops / i8_peak if i8_peak > 0 else None,
+                           "peak_note": "tcgen05.mma kind::i8, M=128 N=256 K=32, operands resident in shared memory, one CTA per SM, measured in this run with CUDA events (gmoe_i8_peak)",
+                           "frac_of_2x_bf16_burst": gu_tops / (2.0 * pk["bf16_tflops"]), "frac_of_2x_bf16_sustained": gu_tops / (2.0 * pk["bf16_tflops_sustained"])},
                 "bf16_peaks_source": pk["src"], "weights_gbs": 256 * 2 * 264192 / gu_t / 1e9}
 
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
