@@ -49,6 +49,16 @@ double gmoe_moe(int L, const float *x, int nb, float *y, const float *bias);
 /* Host in/out: per layer hn = rmsnorm(x, post_ln), x += moe(hn) (maple.c:733-834).  Returns the seconds on the
  * device timeline from the start of the host-to-device copy of x to the end of the copy back. */
 double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias);
+/* The same without waiting, for hosts that stream chunks: gmoe_forward_submit queues the copy of x_in (pinned host memory) to the
+ * card, the layers and the copy of the result to x_out (pinned; may be x_in) and returns; at most two chunks may be outstanding, so that
+ * one chunk's copies run beside the other's kernels (three streams, two staging slots on the card).  gmoe_forward_wait waits for the
+ * oldest outstanding chunk; its x_out is then complete.  It returns the seconds on the device timeline from the last gmoe_forward_mark
+ * (or the first submit) to the end of that chunk's copy back, or a negative value.  After gmoe_ep_init the expert-parallel layer loop
+ * runs (every rank submits and waits alike).  Other entry points must not be called while chunks are outstanding.  No counterpart in
+ * the reference (maple.c:1015-1023 waits for every call). */
+int gmoe_forward_submit(const float *x_in, float *x_out, int nb, int l0, int nl, const float *bias);
+double gmoe_forward_wait(void);
+int gmoe_forward_mark(void);
 /* Device-resident form: upload once, run (asynchronous, on the library's stream), download. */
 int gmoe_x_upload(const float *x, int nb);
 int gmoe_x_download(float *x, int nb);

@@ -592,6 +592,92 @@ double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias) {   /* 
     S.nb_cur = nb;
     return finish("gmoe");
 }
+/* ---- host in / host out without waiting: up to two chunks outstanding (see gmoe.h) ------------------------------------
+ * A chunk goes host -> xin[k] on one copy stream, xin[k] -> x, the layer loop, x -> xout[k] on the library's stream, xout[k] -> host on
+ * a second copy stream; k alternates.  Events order the three streams and guard the two staging slots against their reuse. */
+static struct {
+    cudaStream_t in, out; int ready, seq, done;          /* seq: chunks submitted, done: chunks waited for */
+    float *xin[2], *xout[2]; size_t cap;                /* staging slots on the card, cap floats each */
+    cudaEvent_t mark, start[2], loaded[2], taken[2], ran[2], stored[2];
+    int *h_err;                                          /* pinned: the kernels' error word as each chunk left it */
+} PIPE;
+static int pipe_setup(int nb) {
+    if (!PIPE.ready) {
+        CU("gmoe", cudaStreamCreateWithFlags(&PIPE.in, cudaStreamNonBlocking)); CU("gmoe", cudaStreamCreateWithFlags(&PIPE.out, cudaStreamNonBlocking));
+        CU("gmoe", cudaEventCreate(&PIPE.mark));
+        for (int k = 0; k < 2; k++) {
+            CU("gmoe", cudaEventCreate(&PIPE.start[k])); CU("gmoe", cudaEventCreate(&PIPE.stored[k]));
+            CU("gmoe", cudaEventCreateWithFlags(&PIPE.loaded[k], cudaEventDisableTiming)); CU("gmoe", cudaEventCreateWithFlags(&PIPE.taken[k], cudaEventDisableTiming));
+            CU("gmoe", cudaEventCreateWithFlags(&PIPE.ran[k], cudaEventDisableTiming));
+        }
+        if (cudaHostAlloc((void **)&PIPE.h_err, 2 * sizeof(int), cudaHostAllocDefault) != cudaSuccess) return fail("gmoe", "no pinned memory");
+        PIPE.h_err[0] = PIPE.h_err[1] = 0;
+        CU("gmoe", cudaEventRecord(PIPE.mark, PIPE.in));
+        PIPE.ready = 1;
+    }
+    const size_t need = (size_t)nb * HID;
+    if (need > PIPE.cap) {
+        if (PIPE.seq != PIPE.done) return fail("gmoe", "a larger chunk while chunks are outstanding");
+        for (int k = 0; k < 2; k++) { cudaFree(PIPE.xin[k]); cudaFree(PIPE.xout[k]); PIPE.xin[k] = PIPE.xout[k] = NULL; }
+        PIPE.cap = 0;
+        for (int k = 0; k < 2; k++)
+            if (dmalloc((void **)&PIPE.xin[k], need * 4) || dmalloc((void **)&PIPE.xout[k], need * 4)) return fail("gmoe", "no device memory for the staging slots of %d tokens", nb);
+        PIPE.cap = need;
+    }
+    return 0;
+}
+static int ep_layer_scales(int L);
+int gmoe_forward_submit(const float *x_in, float *x_out, int nb, int l0, int nl, const float *bias) {
+    if (!S.ready) return fail("gmoe", "not initialised");
+    if (PIPE.seq - PIPE.done >= 2) return fail("gmoe", "two chunks are outstanding: gmoe_forward_wait first");
+    g_ep_call = S.ep_on;
+    for (int L = l0; L < l0 + nl; L++) if (check_call("gmoe", L, nb) || (S.ep_on && ep_layer_scales(L))) { g_ep_call = 0; return -1; }
+    g_ep_call = 0;
+    if (pipe_setup(nb)) return -1;
+    const float *bd = bias_dev(bias);
+    const int k = PIPE.seq & 1; const size_t bytes = (size_t)nb * HID * 4;
+    if (PIPE.seq >= 2) CU("gmoe", cudaStreamWaitEvent(PIPE.in, PIPE.taken[k], 0));           /* the slot's previous chunk has been moved into x */
+    CU("gmoe", cudaEventRecord(PIPE.start[k], PIPE.in));
+    CU("gmoe", cudaMemcpyAsync(PIPE.xin[k], x_in, bytes, cudaMemcpyHostToDevice, PIPE.in));
+    CU("gmoe", cudaEventRecord(PIPE.loaded[k], PIPE.in));
+    CU("gmoe", cudaStreamWaitEvent(S.st, PIPE.loaded[k], 0));
+    CU("gmoe", cudaMemcpyAsync(S.x, PIPE.xin[k], bytes, cudaMemcpyDeviceToDevice, S.st));
+    CU("gmoe", cudaEventRecord(PIPE.taken[k], S.st));
+    if (layers_enqueue_ep(nb, l0, nl, bd, S.ep_on)) return -1;
+    if (PIPE.seq >= 2) CU("gmoe", cudaStreamWaitEvent(S.st, PIPE.stored[k], 0));             /* the slot's previous result has left the card */
+    CU("gmoe", cudaMemcpyAsync(PIPE.xout[k], S.x, bytes, cudaMemcpyDeviceToDevice, S.st));
+    CU("gmoe", cudaEventRecord(PIPE.ran[k], S.st));
+    CU("gmoe", cudaStreamWaitEvent(PIPE.out, PIPE.ran[k], 0));
+    CU("gmoe", cudaMemcpyAsync(x_out, PIPE.xout[k], bytes, cudaMemcpyDeviceToHost, PIPE.out));
+    CU("gmoe", cudaMemcpyAsync(&PIPE.h_err[k], S.err, 4, cudaMemcpyDeviceToHost, PIPE.out));
+    CU("gmoe", cudaEventRecord(PIPE.stored[k], PIPE.out));
+    S.nb_cur = nb; PIPE.seq++;
+    return 0;
+}
+double gmoe_forward_wait(void) {
+    if (!PIPE.ready || PIPE.seq == PIPE.done) { fail("gmoe", "gmoe_forward_wait: nothing outstanding"); return -1.0; }
+    const int k = PIPE.done & 1;
+    PIPE.done++;
+    cudaError_t e = cudaEventSynchronize(PIPE.stored[k]);
+    if (e != cudaSuccess) { fail("gmoe", "%s", cudaGetErrorString(e)); return -1.0; }
+    if (PIPE.h_err[k]) {
+        const int code = PIPE.h_err[k];
+        PIPE.h_err[k] = 0; cudaStreamSynchronize(S.st); cudaMemsetAsync(S.err, 0, 4, S.st); cudaMemsetAsync(S.wire, 0, WIRE_BYTES((size_t)S.maxp), S.st);
+        fail("gmoe", "a kernel gave up waiting (code %d); results are invalid", code);
+        return -1.0;
+    }
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, PIPE.mark, PIPE.stored[k]) != cudaSuccess) { fail("gmoe", "event timing"); return -1.0; }
+    return (double)ms * 1e-3;
+}
+int gmoe_forward_mark(void) {
+    if (!S.ready) return fail("gmoe", "not initialised");
+    if (pipe_setup(1)) return -1;
+    if (PIPE.seq != PIPE.done) return fail("gmoe", "gmoe_forward_mark with chunks outstanding");
+    CU("gmoe", cudaStreamSynchronize(S.st)); CU("gmoe", cudaStreamSynchronize(PIPE.out));
+    CU("gmoe", cudaEventRecord(PIPE.mark, PIPE.in));
+    return 0;
+}
 int gmoe_post_norm(int L, int nb, float *logits) {
     if (check_call("gmoe", L, nb)) return -1;
     LayerDev *l = &S.ly[L];

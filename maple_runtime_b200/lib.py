@@ -35,7 +35,7 @@ DECLS = {
     # include/gmoe.h
     "gmoe_init": (i32, [i32]), "gmoe_set_device": (i32, [i32]),
     "gmoe_set_layer": (i32, [i32, vp, vp, vp, vp]), "gmoe_synth_layer": (i32, [u64, i32, i32, i32]),
-    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]),
+    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]), "gmoe_forward_submit": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_forward_wait": (f64, []), "gmoe_forward_mark": (i32, []),
     "gmoe_x_upload": (i32, [vp, i32]), "gmoe_x_download": (i32, [vp, i32]),
     "gmoe_forward_dev": (i32, [i32, i32, i32, vp]),
     "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),

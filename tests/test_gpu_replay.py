@@ -99,3 +99,44 @@ def test_default_router_replay_layer_by_layer(nb, nl, stream, lean, reference, w
     g.set_router(1)
     for L in range(nl):
         g.synth_layer(SEED, L)
+
+
+def test_streamed_chunks_equal_the_waiting_call(lean, weights):
+    """gmoe_forward_submit / gmoe_forward_wait (two chunks outstanding: one chunk's copies beside the other's kernels) against
+    gmoe_forward on the same chunks: same bits, in order, also when input and output are the same pinned buffer; a third submit
+    without a wait and a wait with nothing outstanding are refused and leave the pipeline usable."""
+    import ctypes as C
+    g = lean
+    clib = g.lib
+    nl = 2
+    for L in range(nl):
+        g.synth_layer(SEED + 5, L)
+    for nb in (700, 2048, 64):
+        chunks = [weights.hidden(920 + c, nb) for c in range(5)]
+        want = []
+        for x in chunks:
+            y = x.copy(); g.forward(y, 0, nl); want.append(y)
+        bytes_ = nb * 2048 * 4
+        pin = [clib.gmoe_pinned_alloc(bytes_) for _ in range(4)]             # two inputs, two outputs
+        try:
+            view = [np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(nb, 2048)) for p in pin]
+            assert clib.gmoe_forward_mark() == 0
+            last = 0.0
+            for i, x in enumerate(chunks):
+                view[i % 2][:] = x
+                g._chk(clib.gmoe_forward_submit(pin[i % 2], pin[2 + i % 2], nb, 0, nl, None))
+                if i == 1:
+                    assert clib.gmoe_forward_submit(pin[0], pin[2], nb, 0, nl, None) < 0        # two are outstanding
+                if i >= 1:
+                    t = g._chk(clib.gmoe_forward_wait())
+                    assert t > last; last = t
+                    assert same_bits(view[2 + (i - 1) % 2], want[i - 1]), f"chunk {i - 1} of {nb} tokens"
+            g._chk(clib.gmoe_forward_wait())
+            assert same_bits(view[2 + (len(chunks) - 1) % 2], want[-1])
+            assert clib.gmoe_forward_wait() < 0                                                  # nothing outstanding
+            view[0][:] = chunks[0]                                                               # in place
+            g._chk(clib.gmoe_forward_submit(pin[0], pin[0], nb, 0, nl, None)); g._chk(clib.gmoe_forward_wait())
+            assert same_bits(view[0], want[0])
+        finally:
+            for p in pin:
+                clib.gmoe_pinned_free(p)
