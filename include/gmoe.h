@@ -59,6 +59,15 @@ double gmoe_forward(float *x, int nb, int l0, int nl, const float *bias);
 int gmoe_forward_submit(const float *x_in, float *x_out, int nb, int l0, int nl, const float *bias);
 double gmoe_forward_wait(void);
 int gmoe_forward_mark(void);
+
+/* on = 1: the reference-shaped calls (gpre_moe, gfull_begin, gfull_read) page-lock a host buffer of 1 MB or more where it lies when
+ * they see it a second time at the same address and length, and leave it so: maple.c keeps its hidden-state arrays for the life of the
+ * process (HNB, YB, maple.c:763), and copies from and to page-locked memory run at several times the rate of pageable memory.
+ * on = 0 (default) releases every such registration and stops making new ones.  GPRE_PIN_HOST=1 in the environment turns the policy on
+ * for a host whose source is not touched.  Only for hosts that do not free those buffers while the library may still see them: memory
+ * mapped later at a freed, still registered address would be read through the old pages.  No counterpart in the reference (its card
+ * path shares memory with the host). */
+int gpre_pin_policy(int on);
 /* Device-resident form: upload once, run (asynchronous, on the library's stream), download. */
 int gmoe_x_upload(const float *x, int nb);
 int gmoe_x_download(float *x, int nb);

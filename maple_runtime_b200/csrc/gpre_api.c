@@ -688,6 +688,43 @@ int gmoe_post_norm(int L, int nb, float *logits) {
     return 0;
 }
 
+/* ---- page-locking the host's own buffers ---------------------------------------------------------------------------
+ * The reference's card path reads and writes the host's hidden-state arrays in place (unified memory, gpu_pre.m:318-385); here they cross
+ * PCIe, and from pageable memory that runs at a quarter of the link's rate.  maple.c holds those arrays for the life of the process
+ * (HNB, YB: static).  With the policy on (gpre_pin_policy(1), or GPRE_PIN_HOST=1 in the environment when the library initialises: no
+ * change to the host's source), a buffer of 1 MB or more that a reference-shaped call sees a second time at the same address and length
+ * is page-locked where it lies (cudaHostRegister) and stays so; the copies then run at the rate of pinned memory.  A registration that
+ * fails is forgotten and the buffer stays pageable.  Off by default: a host that frees a registered buffer and maps new memory at the
+ * same address would have the card read the old pages.  Turning the policy off releases every registration. */
+#define PIN_SLOTS 64
+static struct { const void *p; size_t len; int seen, pinned; } PIN[PIN_SLOTS];
+static int pin_on = -1;      /* -1: not decided yet (the environment is read at the first call) */
+int gpre_pin_policy(int on) {
+    pin_on = on != 0;
+    if (!pin_on) {
+        if (S.ready) cudaStreamSynchronize(S.st);
+        for (int i = 0; i < PIN_SLOTS; i++) { if (PIN[i].pinned && cudaHostUnregister((void *)PIN[i].p) != cudaSuccess) cudaGetLastError(); }
+        memset(PIN, 0, sizeof PIN);
+    }
+    return 0;
+}
+static void host_buffer_seen(const void *p, size_t len) {
+    if (pin_on < 0) { const char *e = getenv("GPRE_PIN_HOST"); pin_on = e && e[0] == '1'; }
+    if (!pin_on || !p || len < (1u << 20)) return;
+    int free_i = -1;
+    for (int i = 0; i < PIN_SLOTS; i++) {
+        if (PIN[i].p == p && PIN[i].len == len) {
+            if (!PIN[i].pinned && PIN[i].seen == 1) {
+                PIN[i].seen = 2;
+                if (cudaHostRegister((void *)p, len, cudaHostRegisterDefault) == cudaSuccess) PIN[i].pinned = 1; else cudaGetLastError();
+            }
+            return;
+        }
+        if (!PIN[i].p && free_i < 0) free_i = i;
+    }
+    if (free_i >= 0) { PIN[free_i].p = p; PIN[free_i].len = len; PIN[free_i].seen = 1; PIN[free_i].pinned = 0; }
+}
+
 /* ---- the reference-shaped calls: grouping supplied by the host ---------------------------------------------------- */
 static int upload_grouping(const char *who, int nb, int nu, const uint32_t *loc, const int *regs, const int *ustart,
                            const int *ptok, const float *pw, const int *tp) {
@@ -740,6 +777,7 @@ double gpre_moe(const float *x, int nb, int nu, const uint32_t *loc, const int *
                 const int *ustart, const int *ptok, const float *pw, const int *tp, float *y) {
     (void)next;
     if (upload_grouping("gpre", nb, nu, loc, regs, ustart, ptok, pw, tp)) return -1.0;
+    host_buffer_seen(x, (size_t)nb * HID * 4); host_buffer_seen(y, (size_t)nb * HID * 4);
     CUD("gpre", cudaMemcpyAsync(S.hn, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st));
     cudaEventRecord(S.e0, S.st);
     k_norm_prep(S.st, S.hn, NULL, S.hn, S.hq, S.hqs, S.hqsum, nb);
@@ -754,6 +792,7 @@ double gpre_moe(const float *x, int nb, int nu, const uint32_t *loc, const int *
 void gfull_begin(const float *x, int nb, int pos0) {
     (void)pos0;
     if (!S.ready || nb < 1 || nb > S.maxtok) { fail("gfull", "gfull_begin with %d tokens", nb); return; }
+    host_buffer_seen(x, (size_t)nb * HID * 4);
     cudaMemcpyAsync(S.x, x, (size_t)nb * HID * 4, cudaMemcpyHostToDevice, S.st); S.nb_cur = nb;
 }
 void gfull_moe(int nu, const uint32_t *loc, const int *regs, const int *ustart, const int *ptok, const float *pw, const int *tp) {
@@ -769,7 +808,7 @@ void gfull_moe(int nu, const uint32_t *loc, const int *regs, const int *ustart, 
 void gfull_read(float *x, const uint16_t **ko) {
     if (ko) *ko = NULL;
     if (!S.ready) { fail("gfull", "not initialised"); return; }
-    if (x) cudaMemcpyAsync(x, S.x, (size_t)S.nb_cur * HID * 4, cudaMemcpyDeviceToHost, S.st);
+    if (x) { host_buffer_seen(x, (size_t)S.nb_cur * HID * 4); cudaMemcpyAsync(x, S.x, (size_t)S.nb_cur * HID * 4, cudaMemcpyDeviceToHost, S.st); }
     cudaError_t e = cudaStreamSynchronize(S.st);
     if (e != cudaSuccess) fail("gfull", "%s", cudaGetErrorString(e));
     else if (S.fwd_timed) { float ms = 0; cudaEventElapsedTime(&ms, S.e0, S.e1); S.t_experts += ms * 1e-3; S.fwd_timed = 0; }

@@ -35,7 +35,7 @@ DECLS = {
     # include/gmoe.h
     "gmoe_init": (i32, [i32]), "gmoe_set_device": (i32, [i32]),
     "gmoe_set_layer": (i32, [i32, vp, vp, vp, vp]), "gmoe_synth_layer": (i32, [u64, i32, i32, i32]),
-    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]), "gmoe_forward_submit": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_forward_wait": (f64, []), "gmoe_forward_mark": (i32, []),
+    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]), "gmoe_forward_submit": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_forward_wait": (f64, []), "gmoe_forward_mark": (i32, []), "gpre_pin_policy": (i32, [i32]),
     "gmoe_x_upload": (i32, [vp, i32]), "gmoe_x_download": (i32, [vp, i32]),
     "gmoe_forward_dev": (i32, [i32, i32, i32, vp]),
     "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),
@@ -148,9 +148,9 @@ class Gpre:
         return y, t
 
     # --- compute
-    def gpre_moe(self, x, nu, loc, regs, ustart, ptok, pw, tp):
+    def gpre_moe(self, x, nu, loc, regs, ustart, ptok, pw, tp, out=None):
         nb = x.shape[0]
-        y = np.empty((nb, 2048), np.float32)
+        y = np.empty((nb, 2048), np.float32) if out is None else out
         t = self.lib.gpre_moe(_p(x), nb, nu, _p(loc), _p(regs), None, _p(ustart), _p(ptok), _p(pw), _p(tp), _p(y))
         self._chk(t)
         return y, t

@@ -461,3 +461,29 @@ def test_timed_path_int8_rows_equal_the_kept_stages_path(nb, stream, layers, ora
             continue
         q, qs, qsum = oracle.prep(act[a])
         assert np.array_equal(q, want["aq"].reshape(P, 512)[a]) and np.float32(qs).tobytes() == want["aqs"].reshape(P)[a].tobytes() and qsum == want["aqsum"].reshape(P)[a]
+
+
+def test_gpre_moe_page_locks_buffers_it_sees_again(layers, clib, oracle, weights):
+    """gpre_moe with the same host arrays call after call (maple.c's HNB and YB) and the page-locking policy on: from the second call on
+    they are page-locked in place; the results stay the bits of a call on fresh arrays, with the policy on, off (registrations released)
+    and on again."""
+    from maple_runtime_b200 import lib as ml
+    g = layers
+    nb = 640
+    x = weights.hidden(831, nb)
+    g.forward(x.copy(), 0, 1)
+    nu = int(g.peek("nu", nb)[0]); ue = g.peek("ue", nb)[:nu]
+    args = (nu, np.ascontiguousarray(ml.gloc_for_contiguous()[ue]), np.array([g.layer_region[0], -1, -1, -1], np.int32), g.peek("ustart", nb)[:nu + 1].copy(),
+            g.peek("utok", nb).copy(), g.peek("uw", nb).copy(), g.peek("tp", nb).copy())
+    hn = g.peek("hn", nb).copy()
+    want, _ = g.gpre_moe(hn.copy(), *args)
+    hnb, yb = np.empty_like(hn), np.empty_like(hn)
+    try:
+        for policy in (1, 0, 1):
+            assert clib.gpre_pin_policy(policy) == 0
+            for call in range(3):
+                hnb[:] = hn; yb[:] = 0
+                g.gpre_moe(hnb, *args, out=yb)
+                assert same_bits(yb, want), f"policy {policy}, call {call}"
+    finally:
+        clib.gpre_pin_policy(0)             # releases the registrations before the arrays are freed
