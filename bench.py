@@ -427,8 +427,34 @@ def main():
     # ---- decode shape: 64 conversations x 1 token, one layer at a time over all layers (HBM-bound) ----
     if world > 1:
         out["ep_received_pairs_last_layer"] = [int(v) for v in gather_obj(dist)(clib.gmoe_ep_received())]
+        if not args.zipf:
+            # the same step with skewed routing (a per-expert logit bias from a Zipf(s=1.2) ranking over a seeded permutation): every rank
+            # waits for the rank whose experts are the busiest; not the headline configuration
+            zb = ml.synth_zipf_bias(clib, SEED); zp = zb.ctypes.data
+            for i in range(3):
+                g._chk(clib.gmoe_ep_forward_dev(i % nring, NB, 0, nl, zp)); g._chk(clib.gmoe_sync())
+            barrier(dist)
+            tz, nz = 0.0, min(args.steps, 5)
+            for i in range(nz):
+                g._chk(clib.gmoe_ep_forward_dev(i % nring, NB, 0, nl, zp)); tz += g._chk(clib.gmoe_sync())
+            barrier(dist)
+            tz = allmax(dist, tz)
+            recv = [int(v) for v in gather_obj(dist)(clib.gmoe_ep_received())]
+            out["skewed_routing"] = {"value": world * NB * nz / tz, "unit": UNIT, "ms_per_step": tz / nz * 1e3, "steps": nz,
+                                     "routing": "router logits + per-expert bias ln(256 p_e), p_e ~ rank^-1.2 over a seeded permutation; experts sharded contiguously by index",
+                                     "ep_received_pairs_last_layer": recv}
     if rank == 0 and world == 1:
         out["e2e_gpre_moe"] = gpre_moe_leg(g, ml, nl, 1, min(args.steps, 5))
+        # the head of the attention half (q/k norm, half-rotary embedding, fp16 cache rows): one launch per layer, bound by HBM
+        rng = np.random.default_rng(SEED)
+        qkv = rng.standard_normal((NB, 3072)).astype(np.float32); pos = np.arange(NB, dtype=np.int32)
+        ang = np.arange(NB)[:, None] / np.power(10000.0, (2.0 * np.arange(32)) / 64)[None, :]
+        g.rope_table(np.stack([np.cos(ang), np.sin(ang)], -1).astype(np.float32))
+        ones = np.ones(128, np.float32)
+        ts = sorted(g.qk_rope(qkv, pos, 0, ones, ones)[3] for _ in range(7))
+        ah_bytes = NB * (3072 * 4 + 2048 * 4 + 2 * 512 * 2)
+        out["attention_head"] = {"what": "gmoe_qk_rope on one 2048-token chunk: q/k RMS norm, half-rotary embedding, fp16 key and value rows (kernel only, median of 7)",
+                                 "us": ts[3] * 1e6, "algorithmic_bytes": ah_bytes, "achieved_gbs": ah_bytes / ts[3] / 1e9, "frac_of_measured_hbm": ah_bytes / ts[3] / 1e9 / pk["hbm_gbs"]}
     if not args.no_decode and rank == 0 and world == 1:
         out["decode"] = decode_leg(g, clib, ml, nl, pk, warm, args.steps)
         out["dense_projections"] = dense_leg(g, ml, pk, warm, args.steps)

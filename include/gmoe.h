@@ -68,6 +68,18 @@ int gmoe_forward_mark(void);
  * mapped later at a freed, still registered address would be read through the old pages.  No counterpart in the reference (its card
  * path shares memory with the host). */
 int gpre_pin_policy(int on);
+
+/* ---- the head of the attention half of a layer, on the card (the reference's kernel `qkn`, gpu_full.metal:32-71; its CPU form
+ * maple.c:711-717).  Per token and head: RMS norm of the 16 query and 4 key heads (head dimension 128; qn, kn [128] fp32 as gfull_init
+ * receives them, maple.c:1148), on local layers (glob == 0) the half-rotary embedding at the token's position (dimensions 0..63 as pairs
+ * (i, i + 32), maple.c:403-411) with cos and sin from the table the host builds for gfull_init (maple.c:1151-1153:
+ * cs[position][32][2] = (cos, sin), handed over once with gmoe_rope_table), queries out in fp32, keys and values out in fp16 (the rows
+ * the KV cache receives, maple.c:716-717).  qkv [nb][3072] = q 2048 | k 512 | v 512 (the q,k,v projections' output, gpre_dense group 2L);
+ * pos [nb]; q [nb][2048]; kc, vc [nb][512] fp16.  Host pointers, synchronous; returns the kernel's seconds or a negative value.  Results
+ * are the compiled reference's bits.  This is the first piece of the attention half; attention itself, the cache and the output head
+ * are not on the card (gfull_init answers "unavailable"). */
+int gmoe_rope_table(const float *cs, int positions);
+double gmoe_qk_rope(const float *qkv, const int *pos, int nb, int glob, const float *qn, const float *kn, float *q, uint16_t *kc, uint16_t *vc);
 /* Device-resident form: upload once, run (asynchronous, on the library's stream), download. */
 int gmoe_x_upload(const float *x, int nb);
 int gmoe_x_download(float *x, int nb);

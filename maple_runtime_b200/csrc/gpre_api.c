@@ -901,6 +901,45 @@ int gfull_init(int ctx, int maxtok, int win, const float *norms, const uint16_t 
     fprintf(stderr, "gfull: attention on the card is not part of this library\n"); return -1;
 }
 double gfull_attn(int L, int glob, float *rl) { (void)L; (void)glob; (void)rl; return 0.0; }
+/* ---- the head of the attention half on the card: q/k norm, rotary embedding, fp16 cache rows (see gmoe.h) -------------------- */
+static struct { float *cs; int positions; float *qkv, *q, *norms; void *kc, *vc; int *pos; int cap; } AT;
+int gmoe_rope_table(const float *cs, int positions) {
+    if (!S.ready) return fail("gmoe", "not initialised");
+    if (!cs || positions < 1 || positions > (1 << 20)) return fail("gmoe", "rope table of %d positions", positions);
+    CU("gmoe", cudaStreamSynchronize(S.st));
+    if (AT.cs) { cudaFree(AT.cs); AT.cs = NULL; AT.positions = 0; }
+    if (dmalloc((void **)&AT.cs, (size_t)positions * 64 * 4)) return fail("gmoe", "no device memory for the rope table");
+    CU("gmoe", cudaMemcpyAsync(AT.cs, cs, (size_t)positions * 64 * 4, cudaMemcpyHostToDevice, S.st)); CU("gmoe", cudaStreamSynchronize(S.st));
+    AT.positions = positions; return 0;
+}
+double gmoe_qk_rope(const float *qkv, const int *pos, int nb, int glob, const float *qn, const float *kn, float *q, uint16_t *kc, uint16_t *vc) {
+    if (!S.ready) { fail("gmoe", "not initialised"); return -1.0; }
+    if (nb < 1 || nb > S.maxtok) { fail("gmoe", "gmoe_qk_rope: %d tokens outside 1..%d", nb, S.maxtok); return -1.0; }
+    if (!qkv || !pos || !qn || !kn || !q || !kc || !vc) { fail("gmoe", "gmoe_qk_rope: null argument"); return -1.0; }
+    if (!glob && !AT.cs) { fail("gmoe", "gmoe_qk_rope on a local layer before gmoe_rope_table"); return -1.0; }
+    if (!glob) for (int b = 0; b < nb; b++) if (pos[b] < 0 || pos[b] >= AT.positions) { fail("gmoe", "gmoe_qk_rope: position %d of token %d outside the table (%d positions)", pos[b], b, AT.positions); return -1.0; }
+    if (nb > AT.cap) {
+        cudaStreamSynchronize(S.st);
+        cudaFree(AT.qkv); cudaFree(AT.q); cudaFree(AT.kc); cudaFree(AT.vc); cudaFree(AT.pos); cudaFree(AT.norms); AT.cap = 0;
+        AT.qkv = AT.q = AT.norms = NULL; AT.kc = AT.vc = NULL; AT.pos = NULL;
+        const size_t T = (size_t)S.maxtok;
+        if (dmalloc((void **)&AT.qkv, T * 3072 * 4) || dmalloc((void **)&AT.q, T * 2048 * 4) || dmalloc(&AT.kc, T * 512 * 2) || dmalloc(&AT.vc, T * 512 * 2) ||
+            dmalloc((void **)&AT.pos, T * 4) || dmalloc((void **)&AT.norms, 256 * 4)) { fail("gmoe", "no device memory for the attention head of %d tokens", S.maxtok); return -1.0; }
+        AT.cap = S.maxtok;
+    }
+    CUD("gmoe", cudaMemcpyAsync(AT.qkv, qkv, (size_t)nb * 3072 * 4, cudaMemcpyHostToDevice, S.st));
+    CUD("gmoe", cudaMemcpyAsync(AT.pos, pos, (size_t)nb * 4, cudaMemcpyHostToDevice, S.st));
+    CUD("gmoe", cudaMemcpyAsync(AT.norms, qn, 128 * 4, cudaMemcpyHostToDevice, S.st));
+    CUD("gmoe", cudaMemcpyAsync(AT.norms + 128, kn, 128 * 4, cudaMemcpyHostToDevice, S.st));
+    cudaEventRecord(S.e0, S.st);
+    k_qk_rope(S.st, AT.qkv, AT.pos, nb, glob, AT.norms, AT.norms + 128, AT.cs, AT.positions, AT.q, AT.kc, AT.vc, S.err);
+    cudaEventRecord(S.e1, S.st);
+    CUD("gmoe", cudaMemcpyAsync(q, AT.q, (size_t)nb * 2048 * 4, cudaMemcpyDeviceToHost, S.st));
+    CUD("gmoe", cudaMemcpyAsync(kc, AT.kc, (size_t)nb * 512 * 2, cudaMemcpyDeviceToHost, S.st));
+    CUD("gmoe", cudaMemcpyAsync(vc, AT.vc, (size_t)nb * 512 * 2, cudaMemcpyDeviceToHost, S.st));
+    return finish("gmoe");
+}
+
 /* ---- the attention projections (gpu_pre.m:200-256): every layer's q,k,v (group 2L) and o (group 2L+1) resident on the card.
  * y[nb][rows of the group] = the group's matrices times prep(x[nb][2048]): the expert product with one matrix and all tokens.
  * gpre_dense_add copies into a host staging area (the caller's memory need not outlive the call, as with the reference);

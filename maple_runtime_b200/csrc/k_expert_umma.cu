@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(640, 1) expert_umma_kernel(ExpertArgs a, const
         };
         if (blockIdx.x < nitems) scales_load(ep1, blockIdx.x);
         for (int item = blockIdx.x; item < nitems && live; item += stride, icnt++) {
-            const MoeTile tile = t1; const ExpertPtrs ep = ep1;
+            const MoeTile tile = t1;
             const int mb = item % MB, cnt = tile.cnt, N = (cnt + 15) & ~15;
             const uint32_t buf = icnt % NACC;
             const int r0 = GATEUP ? mb * 128 + row : mb * 256 + 2 * row;      // down: half 0 holds row r0, half 1 row r0 + 1

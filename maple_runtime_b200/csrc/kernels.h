@@ -96,6 +96,11 @@ void k_dense_umma(cudaStream_t st, const ExpertArgs *a, const TMap4 *bmap);
 /* dst[pair] = src[rows[pair]]: 2048-byte int8 rows put into pair (expert-grouped) order */
 void k_gather_rows(cudaStream_t st, const int8_t *src, const int *rows, int8_t *dst, int np);
 
+/* ---- the head of the attention half (k_attn_prep.cu): q/k RMS norm, half-rotary embedding, fp16 keys and values.  qkv [nb][3072]
+ * = q 2048 | k 512 | v 512; pos [nb]; qn, kn [128] fp32; cs [cs_positions][32][2] (cos, sin); q [nb][2048] fp32; kc, vc [nb][512] fp16 */
+void k_qk_rope(cudaStream_t st, const float *qkv, const int *pos, int nb, int glob, const float *qn, const float *kn, const float *cs, int cs_positions,
+               float *q, void *kc, void *vc, int *err);
+
 /* ---- router on the tensor cores (k_router_umma.cu): logits, top-8 and weights of nb tokens.  Tokens whose nine largest logits are
  * too close to call are recomputed in the reference's exact order of operations, so the indices are the reference's for every token;
  * weights and logits of the other tokens agree with it to ~1e-6. */

@@ -35,7 +35,7 @@ DECLS = {
     # include/gmoe.h
     "gmoe_init": (i32, [i32]), "gmoe_set_device": (i32, [i32]),
     "gmoe_set_layer": (i32, [i32, vp, vp, vp, vp]), "gmoe_synth_layer": (i32, [u64, i32, i32, i32]),
-    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]), "gmoe_forward_submit": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_forward_wait": (f64, []), "gmoe_forward_mark": (i32, []), "gpre_pin_policy": (i32, [i32]),
+    "gmoe_moe": (f64, [i32, vp, i32, vp, vp]), "gmoe_forward": (f64, [vp, i32, i32, i32, vp]), "gmoe_forward_submit": (i32, [vp, vp, i32, i32, i32, vp]), "gmoe_forward_wait": (f64, []), "gmoe_forward_mark": (i32, []), "gpre_pin_policy": (i32, [i32]), "gmoe_rope_table": (i32, [vp, i32]), "gmoe_qk_rope": (f64, [vp, vp, i32, i32, vp, vp, vp, vp, vp]),
     "gmoe_x_upload": (i32, [vp, i32]), "gmoe_x_download": (i32, [vp, i32]),
     "gmoe_forward_dev": (i32, [i32, i32, i32, vp]),
     "gmoe_chunks_upload": (i32, [vp, i32, i32]), "gmoe_forward_chunk": (i32, [i32, i32, i32, i32, vp]),
@@ -160,6 +160,19 @@ class Gpre:
         y = np.empty((nb, 2048), np.float32)
         t = self._chk(self.lib.gmoe_moe(L, _p(x), nb, _p(y), _p(bias)))
         return y, t
+
+    def rope_table(self, cs):
+        """cs [positions][32][2] fp32 (cos, sin), as maple.c builds it for gfull_init."""
+        cs = np.ascontiguousarray(cs, np.float32)
+        self._chk(self.lib.gmoe_rope_table(_p(cs), cs.shape[0]))
+
+    def qk_rope(self, qkv, pos, glob, qn, kn):
+        """qkv [nb][3072] fp32, pos [nb] int32, qn/kn [128] fp32 -> q [nb][2048] fp32, kc, vc [nb][512] fp16 bit patterns, seconds."""
+        nb = qkv.shape[0]
+        q = np.empty((nb, 2048), np.float32); kc = np.empty((nb, 512), np.uint16); vc = np.empty((nb, 512), np.uint16)
+        t = self._chk(self.lib.gmoe_qk_rope(_p(np.ascontiguousarray(qkv, np.float32)), _p(np.ascontiguousarray(pos, np.int32)), nb, int(glob),
+                                            _p(np.ascontiguousarray(qn, np.float32)), _p(np.ascontiguousarray(kn, np.float32)), _p(q), _p(kc), _p(vc)))
+        return q, kc, vc, t
 
     def forward(self, x, l0, nl, bias=None):
         """x is updated in place; returns GPU seconds."""

@@ -67,6 +67,40 @@ static void exp_init(void) {
     }
     EXP_READY = 1;
 }
+/* The head of the attention half (maple.c:711-717): RMS norm of the query and key heads (398-402), half-rotary embedding on local layers
+ * (403-411; cos and sin from the table maple.c:1151-1153 builds: cs[pos][32][2]) in the fused forms the reference's compiler emits
+ * (lo = fma(a, cos, -(b sin)), hi = fma(b, cos, a sin): pinned against the compiled reference by tests/test_oracle.py), keys and values
+ * to fp16 with round to nearest even (314-320).  q [nb][16*128], k [nb][4*128] in place; kc, vc [nb][512]. */
+static uint16_t orc_f16(float f) {      /* IEEE binary16, round to nearest even, as vcvtps2ph with rounding mode 0 */
+    uint32_t x; memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u; x &= 0x7FFFFFFFu;
+    if (x >= 0x7F800000u) return (uint16_t)(sign | 0x7C00u | (x > 0x7F800000u ? 0x200u | ((x >> 13) & 0x3FFu) : 0u));
+    if (x >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);                       /* rounds to infinity */
+    if (x < 0x33000001u) return (uint16_t)sign;                                     /* below half of the smallest subnormal */
+    int e = (int)(x >> 23) - 127; uint32_t m = (x & 0x7FFFFFu) | 0x800000u;
+    int shift = e < -14 ? 13 + (-14 - e) : 13;                                      /* subnormal results lose more bits */
+    uint32_t h = m >> shift, rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (h & 1u))) h++;
+    if (e < -14) return (uint16_t)(sign | h);                                       /* h may carry into the smallest normal: same bit pattern */
+    return (uint16_t)(sign | (((uint32_t)(e + 15) << 10) + (h - 0x400u)));          /* a mantissa carry bumps the exponent */
+}
+void orc_qk_rope(float *q, float *k, const float *v, const uint16_t *qn, const uint16_t *kn, const int *pos, const float *cs, int nb, int glob,
+                 uint16_t *kc, uint16_t *vc) {
+    for (int b = 0; b < nb; b++) {
+        for (int h = 0; h < 20; h++) {
+            float *p = h < 16 ? q + ((size_t)b * 16 + h) * 128 : k + ((size_t)b * 4 + (h - 16)) * 128;
+            orc_rmsnorm(p, p, h < 16 ? qn : kn, 128);
+            if (!glob) {
+                const float *t = cs + (size_t)pos[b] * 64;
+                for (int i = 0; i < 32; i++) {
+                    const float a = p[i], bb = p[i + 32], c = t[2 * i], s = t[2 * i + 1];
+                    p[i] = fmaf(a, c, -(bb * s)); p[i + 32] = fmaf(bb, c, a * s);
+                }
+            }
+        }
+        for (int i = 0; i < 512; i++) { kc[(size_t)b * 512 + i] = orc_f16(k[(size_t)b * 512 + i]); vc[(size_t)b * 512 + i] = orc_f16(v[(size_t)b * 512 + i]); }
+    }
+}
 void orc_exp_table(uint64_t *out) { if (!EXP_READY) exp_init(); memcpy(out, EXP_TAB, sizeof EXP_TAB); }
 float orc_expf_model(float x) {
     if (!EXP_READY) exp_init();

@@ -76,6 +76,14 @@ class Oracle:
     def rmsnorm(self, x, w):
         out = np.zeros_like(x); self.lib.orc_rmsnorm(_p(out), _p(x), _p(w), x.shape[-1]); return out
 
+    def qk_rope(self, q, k, v, qn, kn, pos, cs, glob):
+        """maple.c:711-717 on copies: returns q (fp32), k (fp32), kc, vc (fp16 bit patterns)."""
+        nb = q.shape[0]
+        q = np.array(q, np.float32, copy=True); k = np.array(k, np.float32, copy=True)
+        kc = np.zeros((nb, 512), np.uint16); vc = np.zeros((nb, 512), np.uint16)
+        self.lib.orc_qk_rope(_p(q), _p(k), _p(np.ascontiguousarray(v, np.float32)), _p(qn), _p(kn), _p(np.ascontiguousarray(pos, np.int32)), _p(cs), nb, int(glob), _p(kc), _p(vc))
+        return q, k, kc, vc
+
     def router_logits(self, router, hn):
         nb = hn.shape[0]; out = np.zeros((nb, NE), np.float32)
         self.lib.orc_router_logits(_p(router), _p(hn), nb, _p(out)); return out
@@ -132,6 +140,18 @@ class Reference:
         rc = self.lib.rh_moe(L, _p(x), nb, int(norm), _p(y), _p(bias), C.byref(s))
         assert rc == nb * TOPK, rc
         return (x if norm else y), d
+
+    def qk_rope(self, q, k, v, qn, kn, pos, glob):
+        """rmsnorm + rope + to_f16 as step_batch calls them (maple.c:711-717), on copies."""
+        nb = q.shape[0]
+        q = np.array(q, np.float32, copy=True); k = np.array(k, np.float32, copy=True)
+        kc = np.zeros((nb, 512), np.uint16); vc = np.zeros((nb, 512), np.uint16)
+        self.lib.rh_qk_rope(_p(q), _p(k), _p(np.ascontiguousarray(v, np.float32)), _p(qn), _p(kn), _p(np.ascontiguousarray(pos, np.int32)), nb, int(glob), _p(kc), _p(vc))
+        return q, k, kc, vc
+
+    def rope_table(self, positions):
+        """The (cos, sin) table maple.c builds for gfull_init (maple.c:1151-1153)."""
+        cs = np.zeros((positions, 32, 2), np.float32); self.lib.rh_rope_table(_p(cs), positions); return cs
 
     def stack(self, x, l0, nl, bias=None):
         """x updated in place; seconds on the reference's own clock."""

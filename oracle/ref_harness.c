@@ -6,7 +6,8 @@
  * reference's own static functions for the mixture-of-experts half of a layer:
  *   rmsnorm (maple.c:398), prep (184), job_route_small/multi (853/870), job_topk (910),
  *   group_pairs (924), jobB_gateup (471) -> tdot_multi (425), the SiLU*up + prep loop (825-832),
- *   jobB_down (498), the combine loop (834) and the worker pool run()/worker (89-108).
+ *   jobB_down (498), the combine loop (834) and the worker pool run()/worker (89-108);
+ * and for the first step of the attention half: rmsnorm + rope (403-411) + to_f16 (314-320) as step_batch calls them (711-717).
  * Outputs land in oracle/_ref/ only (libmaple_ref.so: IEEE build, the parity pin;
  * libmaple_ref_fast.so: the reference's documented -ffast-math build, the timed CPU baseline).
  */
@@ -132,5 +133,25 @@ double rh_stack(float *x, int nb, int l0, int nlayers, const float *bias) {
     double t0 = now();
     for (int L = l0; L < l0 + nlayers; L++) if (rh_moe(L, x, nb, 1, NULL, bias, NULL) < 0) return -1.0;
     return now() - t0;
+}
+/* The head of the attention half as step_batch runs it (maple.c:711-717): per token, RMS norm of every query and key head with the
+ * layer's q_norm / k_norm, half-rotary embedding at the token's position on local layers (maple.c:403-411), keys and values to fp16
+ * (maple.c:314-320).  q [nb][NH*HD] and k [nb][NKV*HD] are updated in place; kc, vc [nb][NKV*HD] receive the cache rows. */
+void rh_qk_rope(float *q, float *k, const float *v, const uint16_t *qn, const uint16_t *kn, const int *pos, int nb, int glob, uint16_t *kc, uint16_t *vc) {
+    for (int i = 0; i < ROT / 2; i++) INV_FREQ[i] = 1.0 / pow(10000.0, (2.0 * i) / ROT);      /* maple.c:1085 */
+    BF bq = {qn, HD, 1}, bk = {kn, HD, 1};
+    for (int b = 0; b < nb; b++) {
+        for (int h = 0; h < NH; h++) { float *p = q + ((size_t)b * NH + h) * HD; rmsnorm(p, p, &bq, HD); if (!glob) rope(p, pos[b]); }
+        for (int h = 0; h < NKV; h++) { float *p = k + ((size_t)b * NKV + h) * HD; rmsnorm(p, p, &bk, HD); if (!glob) rope(p, pos[b]); }
+        to_f16(kc + (size_t)b * NKV * HD, k + (size_t)b * NKV * HD, NKV * HD);
+        to_f16(vc + (size_t)b * NKV * HD, v + (size_t)b * NKV * HD, NKV * HD);
+    }
+}
+/* the (cos, sin) table maple.c hands to gfull_init (maple.c:1151-1153): cs[pos][32][2] */
+void rh_rope_table(float *cs, int positions) {
+    for (int i = 0; i < ROT / 2; i++) INV_FREQ[i] = 1.0 / pow(10000.0, (2.0 * i) / ROT);
+    for (int pos = 0; pos < positions; pos++) for (int i = 0; i < ROT / 2; i++) {
+        double f = pos * INV_FREQ[i]; cs[(pos * 32 + i) * 2] = (float)cos(f); cs[(pos * 32 + i) * 2 + 1] = (float)sin(f);
+    }
 }
 int rh_bmax(void) { return BMAX; }

@@ -150,3 +150,33 @@ def test_dense_projection_statement_equals_reference_tdot(reference):
         for r in (0, 1, 17, 128, 255):
             got = np.float32(lib.rh_tdot(packed.ctypes.data, scales.ctypes.data, rows, cols, r, xb.ctypes.data))
             assert got.tobytes() == want[b, r].tobytes(), (b, r, got, want[b, r])
+
+
+def attention_head_case(seed, nb):
+    """q, k, v rows of ordinary magnitude plus rows that stress the fp16 conversion (overflow, subnormals, ties), norm weights near 1
+    (bf16), positions over the whole table including 0."""
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((nb, 2048)).astype(np.float32); k = rng.standard_normal((nb, 512)).astype(np.float32)
+    v = rng.standard_normal((nb, 512)).astype(np.float32)
+    if nb > 4:
+        v[1] *= np.float32(1e5); v[2] *= np.float32(1e-6); v[3, ::2] = np.float32(2049.0); v[3, 1::2] = np.float32(6.0e-8)    # inf, subnormal halves, ties
+        k[2] *= np.float32(300.0); q[3] = 0.0
+    qn = ((rng.standard_normal(128) * 0.1 + 1).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    kn = ((rng.standard_normal(128) * 0.1 + 1).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    pos = rng.integers(0, 4096, nb).astype(np.int32); pos[0] = 0
+    return q, k, v, qn, kn, pos
+
+
+@pytest.mark.parametrize("nb,glob,seed", [(1, 0, 41), (33, 0, 42), (33, 1, 43), (257, 0, 44)])
+def test_attention_head_restatement_equals_the_reference(nb, glob, seed, oracle, reference):
+    """q/k RMS norm, half-rotary embedding and the fp16 cache rows (maple.c:711-717): the restatement against the compiled reference, bit
+    for bit, fp32 and fp16 outputs; the rotation's fused multiply-add forms are the ones the reference's compiler chose."""
+    q, k, v, qn, kn, pos = attention_head_case(seed, nb)
+    cs = reference.rope_table(4096)
+    want = reference.qk_rope(q, k, v, qn, kn, pos, glob)
+    got = oracle.qk_rope(q, k, v, qn, kn, pos, cs, glob)
+    for name, a, b in zip(("q", "k", "kc", "vc"), got, want):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), name
+    # the fp16 conversion itself against numpy's round-to-nearest-even
+    with np.errstate(over="ignore"):
+        assert np.array_equal(got[3], v.astype(np.float16).view(np.uint16))
