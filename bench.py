@@ -261,7 +261,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for small profiling captures (not a bench number)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true")
-    ap.add_argument("--capture", choices=["prefill", "decode"], help="a short run for a profiler, no timing and no JSON line: 2 layers, 3 passes of "
+    ap.add_argument("--capture", choices=["prefill", "decode", "attn"], help="a short run for a profiler, no timing and no JSON line: 2 layers, 3 passes of "
                     "one chunk (2048 tokens, or 64 for decode) with plain launches (no graph replay), so that a capture of a few launches of one kernel stays small")
     ap.add_argument("--zipf", action="store_true", help="skewed routing: a per-expert logit bias from a Zipf(s=1.2) ranking (BASELINE config 4); not the headline line")
     args = ap.parse_args()
@@ -272,6 +272,15 @@ def main():
         from maple_runtime_b200 import lib as ml
         nbc = NB if args.capture == "prefill" else 64
         g = ml.Gpre(NB, device=local)
+        if args.capture == "attn":      # the head of the attention half alone: 2048 tokens, local layer, 3 launches
+            rng = np.random.default_rng(SEED)
+            qkv = rng.standard_normal((NB, 3072)).astype(np.float32); pos = np.arange(NB, dtype=np.int32)
+            ang = np.arange(NB)[:, None] / np.power(10000.0, (2.0 * np.arange(32)) / 64)[None, :]
+            g.rope_table(np.stack([np.cos(ang), np.sin(ang)], -1).astype(np.float32))
+            for _ in range(3):
+                g.qk_rope(qkv, pos, 0, np.ones(128, np.float32), np.ones(128, np.float32))
+            print("capture run done: attn, 2048 tokens, 3 launches", file=sys.stderr)
+            return
         for L in range(2):
             g.synth_layer(SEED, L)
         g.lib.gmoe_set_graph(0)
