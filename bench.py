@@ -337,7 +337,6 @@ def main():
     wall = time.perf_counter() - wall0
     barrier(dist)
     launches = clib.gmoe_launch_count() - l0
-    clocks = sampler.summary()
     t_dev = allmax(dist, t_dev)
     value = world * NB * args.steps / t_dev
 
@@ -391,6 +390,7 @@ def main():
     t_e2e = allmax(dist, t_e2e)
     e2e = world * NB * args.steps / t_e2e
     e2e_sync = world * NB * args.steps / t_sync
+    clocks = sampler.summary()          # sampled from the start of the device-timed steps to the end of the host-buffer loops
 
     # ---- roofline of the dominant kernel ----
     pk = peaks()
